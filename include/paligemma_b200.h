@@ -269,6 +269,71 @@ int pg_advance_decode_slots(const int* next, int* tok_ring, int ring, int* cur_t
  * bytes >= 16 (rounded down to a multiple of 16).  Never changes results. */
 int pg_prefetch_l2(const void* ptr, long long bytes, int ctas, int evict_last, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------------
+ * Token-sequence decoders (models/registry: text-only designs served through a ragged step).  A step's rows are the new
+ * tokens of several requests ("entries"): entry e owns rows [entry_row0[e], entry_row0[e] + entry_n[e]) and continues a
+ * sequence of entry_ctx[e] tokens that already sit in the paged cache / the recurrent state.  "act" tensors are bf16
+ * (act_f32 = 0) or fp32 (act_f32 = 1); norms, scores, probabilities, states and residual sums are always fp32.
+ * ------------------------------------------------------------------------------------------------------------------- */
+
+/* out[t, f] = sum_k x[t, k] w[f, k] with plain fp32 FMAs (no tensor-core mode): the exact-precision matrix product of
+ * the fp32 serving mode, and the bf16 product for shapes the TMA kernels cannot take (K or a pitch not a multiple of 8).
+ * in_f32: x and w are fp32 (else bf16); out_f32: out is fp32 (else bf16). */
+int pg_gemm_simt(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int tokens, int features,
+                 int K, int in_f32, int out_f32, void* stream);
+
+/* out[t, 0:D] (fp32) = table[tokens[t], col0 : col0 + D] * scale  (embedding lookup; table bf16 or fp32, pitch ld). */
+int pg_embed_rows(const int* tokens, const void* table, long long ld, int col0, float* out, int rows, int D, float scale,
+                  int table_f32, void* stream);
+
+/* Grouped RMS norm folded into the residual add: r = gnorm(y[t, :]) * w, where the row is cut into `groups` equal
+ * consecutive parts and each part is divided by sqrt(mean(part^2) + eps).  x != NULL: x[t, :] += r in place (fp32 residual
+ * stream); x == NULL: the bare norm.  out_act != NULL also receives the result (new residual or bare norm) in the activation
+ * type -- the operand of the next matrix product. */
+int pg_group_rmsnorm_add(const float* y, long long ldy, const float* w, float* x, void* out_act, int rows, int D, int groups,
+                         float eps, int out_f32, void* stream);
+
+/* out[t, :] = o[t, :] / sqrt(mean(o[t, :]^2) + eps) * w * sigmoid(gate[t, :])   (o fp32 [rows, D]; gate / out: act type). */
+int pg_rmsnorm_gate(const float* o, const float* w, const void* gate, long long ldg, void* out, int rows, int D, float eps,
+                    int act_f32, void* stream);
+
+/* out[t, f] = gelu_tanh(gu[t, f]) * gu[t, F + f]: the gate || up product when it is not fused into the GEMM epilogue. */
+int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int act_f32, void* stream);
+
+/* out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], col0 + j] for j < n, 0 for n <= j < n_pad (per-token side input: a
+ * gate projection of the residual times the token's own low-dimensional embedding slice). */
+int pg_side_gate(const void* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
+                 long long ldo, int rows, int n, int n_pad, int act_f32, void* stream);
+
+/* Softmax-attention front end on the fused projection rows qkv[t] = [q heads | k heads | v heads | ...] (pitch ld):
+ * q and k heads are RMS-normalised over dim with the shared weights q_norm / k_norm, then the first rot_dims dimensions are
+ * rotated in interleaved pairs (2i, 2i+1) by pos[t] * freq[i] (freq: double [rot_dims / 2]); v heads are divided by their
+ * root mean square over vdim.  q goes to q_out [rows, H * dim]; k and v go to cache row
+ * page_table[row_entry[t] * max_pages + pos[t] / page] * page + pos[t] % page of k_pages [.., G * dim] / v_pages [.., G * vdim]. */
+int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
+                    int page, const double* freq, const float* q_norm, const float* k_norm, void* q_out, void* k_pages,
+                    void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int act_f32, void* stream);
+
+/* Causal attention of every entry's new rows over its cached keys / values (query head h reads k/v head h / (H / G)):
+ * s = (q . k) * scale, s <- softcap * tanh(s / softcap) when softcap > 0, softmax over keys 0 .. position, times V; the
+ * result is multiplied by sigmoid(gate[t, h * vdim + c]) when gate != NULL and written to out [rows, H * vdim].
+ * page_table: int32 [entries, max_pages]; max_n = the largest entry_n (sizes the grid). */
+int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
+                   const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
+                   int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream);
+
+/* Decayed linear attention on qkv[t] = [q heads | k heads | v heads | ...] (q, k: H x dim, v: H x vdim; silu applied here):
+ * per head S <- decay[h] * S + k v^T, out[t, h * vdim + :] = S^T q (fp32).  state: fp32 [slots, H, dim, vdim]; entry e
+ * continues state[entry_slot[e]] (from zero when entry_ctx[e] == 0) and leaves its new state there.
+ * pg_linear_attn_scan steps token by token; pg_linear_attn_chunked advances in blocks of 32 tokens (same results up to
+ * fp32 summation order) and is meant for prompt portions. */
+int pg_linear_attn_scan(const void* qkv, long long ld, float* state, const float* decay, float* out, const int* entry_row0,
+                        const int* entry_n, const int* entry_ctx, const int* entry_slot, int entries, int H, int dim, int vdim,
+                        int act_f32, void* stream);
+int pg_linear_attn_chunked(const void* qkv, long long ld, float* state, const float* decay, float* out, const int* entry_row0,
+                           const int* entry_n, const int* entry_ctx, const int* entry_slot, int entries, int H, int dim, int vdim,
+                           int act_f32, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -62,6 +62,17 @@ SIGNATURES = {
     "pg_sample_top_p_stats": [p, i64, p, i64, p, i32, i32, f32, f32, u64, p, p, p],
     "pg_advance_decode": [p, p, p, p, i32, p, i32, p],
     "pg_advance_decode_slots": [p, p, i32, p, p, p, p, i32, p],
+    # token-sequence decoders (ragged steps)
+    "pg_gemm_simt": [p, i64, p, i64, p, i64, i32, i32, i32, i32, i32, p],
+    "pg_embed_rows": [p, p, i64, i32, p, i32, i32, f32, i32, p],
+    "pg_group_rmsnorm_add": [p, i64, p, p, p, i32, i32, i32, f32, i32, p],
+    "pg_rmsnorm_gate": [p, p, p, i64, p, i32, i32, f32, i32, p],
+    "pg_geglu": [p, i64, p, i64, i32, i32, i32, p],
+    "pg_side_gate": [p, i64, p, p, i64, i32, p, i64, i32, i32, i32, i32, p],
+    "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, p],
+    "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, p],
+    "pg_linear_attn_scan": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
+    "pg_linear_attn_chunked": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
 }
 _RESTYPE = {"pg_launch_count": i64}
 

@@ -1,0 +1,246 @@
+// Kernels of the token-sequence decoders (ragged steps: every row is one token of some request) that are not
+// contractions on the tensor cores: exact-precision GEMM (fp32, or bf16 operands of shapes the TMA kernels cannot take),
+// embedding rows, grouped RMS norm folded into the residual add, gated RMS norm, GeGLU product, per-token side input.
+//
+// "act" tensors hold activations in the model's activation type: bf16 (is_f32 = 0) or fp32 (is_f32 = 1).  Norm
+// statistics, the residual stream and every sum are fp32.
+#include "common.cuh"
+#include "paligemma_b200.h"
+
+using bf16 = __nv_bfloat16;
+
+#define PG_ST(s) reinterpret_cast<cudaStream_t>(s)
+#define PG_RET()                                                   \
+  do {                                                             \
+    pg_count_launch(1);                                            \
+    return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA; \
+  } while (0)
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ld_f(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ld_f<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld_f<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T>
+__device__ __forceinline__ void st_f(T* p, long long i, float v);
+template <>
+__device__ __forceinline__ void st_f<float>(float* p, long long i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void st_f<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// block-wide sum of one value per thread; `red` holds at least 32 floats
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// out[t, f] = sum_k x[t, k] * w[f, k]: 64 x 64 output tile per CTA, 16-wide k steps through shared memory, a 4 x 4
+// register tile per thread, plain fp32 FMAs in k order (no reduced-precision tensor mode, no split accumulation).
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x, long long ldx, const TI* __restrict__ w, long long ldw,
+                                                        TO* __restrict__ out, long long ldo, int T, int F, int K) {
+  __shared__ float xs[16][64 + 4];
+  __shared__ float ws[16][64 + 4];
+  const int t0 = blockIdx.y * 64, f0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, k = i & 15;
+      xs[k][r] = (t0 + r < T && k0 + k < K) ? ld_f(x, (long long)(t0 + r) * ldx + k0 + k) : 0.f;
+      ws[k][r] = (f0 + r < F && k0 + k < K) ? ld_f(w, (long long)(f0 + r) * ldw + k0 + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&xs[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = t0 + ty * 4 + i, f = f0 + tx * 4 + j;
+      if (t < T && f < F) st_f(out, (long long)t * ldo + f, acc[i][j]);
+    }
+}
+
+// x[t, :] = table[token[t], col0 : col0 + D] * scale   (fp32 out)
+template <typename TI>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const TI* __restrict__ table, long long ld, int col0, float* __restrict__ out,
+                                  int D, float scale) {
+  const int t = blockIdx.x;
+  const long long row = tokens[t];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[(long long)t * D + d] = ld_f(table, row * ld + col0 + d) * scale;
+}
+
+// Grouped RMS norm of y (fp32) times w, optionally added to the fp32 residual row x (in place); the result (the new residual,
+// or the bare norm when x == NULL) is also written in the activation type when out_act != NULL.  One CTA per row; the
+// row is cut into `groups` equal consecutive parts with their own mean square.
+template <typename TO>
+__global__ void __launch_bounds__(256) group_rmsnorm_add_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ w,
+                                                                float* __restrict__ x, TO* __restrict__ out_act, int D, int groups, float eps) {
+  extern __shared__ float sm[];  // D values + 32 + groups
+  float* row = sm;
+  float* red = sm + D;
+  float* inv = red + 32;
+  const long long t = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) row[d] = y[t * ldy + d];
+  __syncthreads();
+  const int gs = D / groups;
+  for (int g = 0; g < groups; ++g) {
+    float s = 0.f;
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) { const float v = row[g * gs + d]; s = fmaf(v, v, s); }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) inv[g] = 1.0f / sqrtf(s / (float)gs + eps);
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = row[d] * inv[d / gs] * w[d];
+    if (x != nullptr) { v += x[t * D + d]; x[t * D + d] = v; }
+    if (out_act != nullptr) st_f(out_act, t * D + d, v);
+  }
+}
+
+// out[t, :] = rms(o[t, :]) * w * sigmoid(gate[t, :])   (o fp32 [T, D]; gate: activation-type column slice, pitch ldg)
+template <typename TA>
+__global__ void __launch_bounds__(256) rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, const TA* __restrict__ gate,
+                                                           long long ldg, TA* __restrict__ out, int D, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = o[t * D + d]; s = fmaf(v, v, s); }
+  s = block_sum(s, red);
+  const float inv = 1.0f / sqrtf(s / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float g = ld_f(gate, t * ldg + d);
+    st_f(out, t * D + d, o[t * D + d] * inv * w[d] * (1.0f / (1.0f + expf(-g))));
+  }
+}
+
+// out[t, f] = gelu_tanh(gu[t, f]) * gu[t, F + f]    (unfused gate || up product: the exact-precision path)
+template <typename TA>
+__global__ void geglu_kernel(const TA* __restrict__ gu, long long ldgu, TA* __restrict__ out, long long ldo, int F, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / F;
+  const int f = (int)(i % F);
+  st_f(out, t * ldo + f, pg::gelu_tanh(ld_f(gu, t * ldgu + f)) * ld_f(gu, t * ldgu + F + f));
+}
+
+// out[t, j] = gelu_tanh(z[t, j]) * table[token[t], col0 + j]  for j < n, zero for n <= j < n_pad
+template <typename TA>
+__global__ void side_gate_kernel(const TA* __restrict__ z, long long ldz, const int* __restrict__ tokens, const TA* __restrict__ table, long long ldt,
+                                 int col0, TA* __restrict__ out, long long ldo, int n, int n_pad, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / n_pad;
+  const int j = (int)(i % n_pad);
+  float v = 0.f;
+  if (j < n) v = pg::gelu_tanh(ld_f(z, t * ldz + j)) * ld_f(table, (long long)tokens[t] * ldt + col0 + j);
+  st_f(out, t * ldo + j, v);
+}
+
+}  // namespace
+
+extern "C" int pg_gemm_simt(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int tokens, int features,
+                            int K, int in_f32, int out_f32, void* stream) {
+  if (tokens <= 0 || features <= 0 || K <= 0 || x == nullptr || w == nullptr || out == nullptr) return PG_ERR_ARG;
+  dim3 grid((features + 63) / 64, (tokens + 63) / 64);
+  if (grid.y > 65535) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (in_f32 && out_f32)
+    gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K);
+  else if (!in_f32 && out_f32)
+    gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K);
+  else if (!in_f32 && !out_f32)
+    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K);
+  else
+    return PG_ERR_ARG;
+  PG_RET();
+}
+
+extern "C" int pg_embed_rows(const int* tokens, const void* table, long long ld, int col0, float* out, int rows, int D, float scale,
+                             int table_f32, void* stream) {
+  if (rows <= 0 || D <= 0) return PG_ERR_ARG;
+  if (table_f32)
+    embed_rows_kernel<float><<<rows, 128, 0, PG_ST(stream)>>>(tokens, static_cast<const float*>(table), ld, col0, out, D, scale);
+  else
+    embed_rows_kernel<bf16><<<rows, 128, 0, PG_ST(stream)>>>(tokens, static_cast<const bf16*>(table), ld, col0, out, D, scale);
+  PG_RET();
+}
+
+extern "C" int pg_group_rmsnorm_add(const float* y, long long ldy, const float* w, float* x, void* out_act, int rows, int D, int groups,
+                                    float eps, int out_f32, void* stream) {
+  if (rows <= 0 || D <= 0 || groups <= 0 || (D % groups) != 0 || D > 32768) return PG_ERR_ARG;
+  const size_t smem = (D + 32 + groups) * sizeof(float);
+  if (smem > 200 * 1024) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (out_f32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(group_rmsnorm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    group_rmsnorm_add_kernel<float><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<float*>(out_act), D, groups, eps);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(group_rmsnorm_add_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    group_rmsnorm_add_kernel<bf16><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<bf16*>(out_act), D, groups, eps);
+  }
+  PG_RET();
+}
+
+extern "C" int pg_rmsnorm_gate(const float* o, const float* w, const void* gate, long long ldg, void* out, int rows, int D, float eps,
+                               int act_f32, void* stream) {
+  if (rows <= 0 || D <= 0) return PG_ERR_ARG;
+  if (act_f32)
+    rmsnorm_gate_kernel<float><<<rows, 256, 0, PG_ST(stream)>>>(o, w, static_cast<const float*>(gate), ldg, static_cast<float*>(out), D, eps);
+  else
+    rmsnorm_gate_kernel<bf16><<<rows, 256, 0, PG_ST(stream)>>>(o, w, static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), D, eps);
+  PG_RET();
+}
+
+extern "C" int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int act_f32, void* stream) {
+  if (rows <= 0 || F <= 0) return PG_ERR_ARG;
+  const long long total = (long long)rows * F;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act_f32)
+    geglu_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(gu), ldgu, static_cast<float*>(out), ldo, F, total);
+  else
+    geglu_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(gu), ldgu, static_cast<bf16*>(out), ldo, F, total);
+  PG_RET();
+}
+
+extern "C" int pg_side_gate(const void* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
+                            long long ldo, int rows, int n, int n_pad, int act_f32, void* stream) {
+  if (rows <= 0 || n <= 0 || n_pad < n) return PG_ERR_ARG;
+  const long long total = (long long)rows * n_pad;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act_f32)
+    side_gate_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(z), ldz, tokens, static_cast<const float*>(table), ldt, col0,
+                                                              static_cast<float*>(out), ldo, n, n_pad, total);
+  else
+    side_gate_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(z), ldz, tokens, static_cast<const bf16*>(table), ldt, col0,
+                                                             static_cast<bf16*>(out), ldo, n, n_pad, total);
+  PG_RET();
+}

@@ -1,0 +1,168 @@
+"""Sub-layers of the token-sequence decoders, each a mechanism with its constants as parameters.
+
+  GatedSoftmaxAttention   grouped-query softmax attention over the paged cache: per-head q/k RMS norm, partial interleaved
+                          rotary positions with long-wavelength frequency rescaling, weightless value norm, tanh soft cap,
+                          sigmoid output gate
+  LightningAttention      decayed linear attention with a per-sequence fp32 state, gated RMS norm over the joined heads
+  GegluFeedForward        W_down(gelu_tanh(W_gate h) * W_up h)
+  TokenSideInput          a per-layer, per-token low-dimensional embedding gated by a projection of the residual stream
+
+Every sub-layer gets its weights from a name -> tensor dict (`take(name)` pops and checks the shape), packs them once for a
+`Precision`, says what it keeps per sequence (`cache_spec`), and maps the step's rows h [T, D] (activation type) to
+y [T, D] fp32; the block around it owns norms and the residual stream.
+"""
+import math
+
+import torch
+
+from . import _lib, seq_ops
+from .modeling_gemma import PAGE
+
+
+def rotary_frequencies(base: float, dims: int, scaling=None):
+    """f_i = base^(-2i/dims), i < dims/2 (float64).  With `scaling` = dict(factor, low, high, original): wavelengths
+    2 pi / f shorter than original/high keep f, longer than original/low use f / factor, and between the two the blend
+    (1 - s) f / factor + s f with s = (original / wavelength - low) / (high - low)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    if scaling:
+        factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        wl = 2.0 * math.pi / f
+        s = (orig / wl - low) / (high - low)
+        mid = (1.0 - s) * f / factor + s * f
+        f = torch.where(wl < orig / high, f, torch.where(wl > orig / low, f / factor, mid))
+    return f
+
+
+class GatedSoftmaxAttention:
+    def __init__(self, width, heads, kv_heads, dim, vdim, scale, softcap, rot_dims, rot_base, rot_scaling, eps):
+        if heads % kv_heads:
+            raise ValueError("query heads must be a multiple of key/value heads")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError("rotary dimensions must be even and at most the head size")
+        self.D, self.H, self.G, self.dim, self.vdim = width, heads, kv_heads, dim, vdim
+        self.scale, self.softcap, self.rot_dims, self.eps = float(scale), float(softcap or 0.0), int(rot_dims), float(eps)
+        self.freq = rotary_frequencies(rot_base, rot_dims, rot_scaling) if rot_dims else torch.zeros(1, dtype=torch.float64)
+
+    def cache_spec(self):
+        return ("kv", self.G * self.dim, self.G * self.vdim)
+
+    def load(self, take, pre):
+        H, G, dim, vdim, D = self.H, self.G, self.dim, self.vdim, self.D
+        self.w = dict(q=take(pre + "q", (H * dim, D)), k=take(pre + "k", (G * dim, D)), v=take(pre + "v", (G * vdim, D)),
+                      g=take(pre + "g", (H * vdim, D)), o=take(pre + "o", (D, H * vdim)),
+                      qn=take(pre + "q.norm", (dim,)), kn=take(pre + "k.norm", (dim,)))
+
+    def pack(self, prec):
+        w = self.w
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"]], 0).to("cuda", prec.dtype).contiguous()
+        self.w_o = w["o"].to("cuda", prec.dtype).contiguous()
+        self.qn, self.kn = w["qn"].to("cuda", torch.float32), w["kn"].to("cuda", torch.float32)
+        self.freq_d = self.freq.to("cuda")
+
+    def __call__(self, h, b, store, li, prec):
+        H, G, dim, vdim = self.H, self.G, self.dim, self.vdim
+        proj = seq_ops.linear(h, self.w_in, prec.empty(b.T, self.w_in.shape[0]))
+        q = prec.empty(b.T, H * dim)
+        kp, vp = store.k_pages[li], store.v_pages[li]
+        seq_ops.attn_prepare(proj, b, self.freq_d, self.qn, self.kn, q, kp, vp, H, G, dim, vdim, self.rot_dims, self.eps, PAGE)
+        att = prec.empty(b.T, H * vdim)
+        gate = proj[:, (H + G) * dim + G * vdim:]
+        seq_ops.attn_ragged(q, kp, vp, gate, att, b, H, G, dim, vdim, self.scale, self.softcap, PAGE)
+        return seq_ops.linear(att, self.w_o, torch.empty(b.T, self.D, device="cuda", dtype=torch.float32))
+
+
+class LightningAttention:
+    def __init__(self, width, heads, dim, vdim, decay, eps):
+        if len(decay) != heads:
+            raise ValueError("one decay per head")
+        self.D, self.H, self.dim, self.vdim, self.eps = width, heads, dim, vdim, float(eps)
+        self.decay = torch.tensor([float(a) for a in decay], dtype=torch.float32)
+
+    def cache_spec(self):
+        return ("state", (self.H, self.dim, self.vdim))
+
+    def load(self, take, pre):
+        H, dim, vdim, D = self.H, self.dim, self.vdim, self.D
+        self.w = dict(q=take(pre + "q", (H * dim, D)), k=take(pre + "k", (H * dim, D)), v=take(pre + "v", (H * vdim, D)),
+                      g=take(pre + "g", (H * vdim, D)), o=take(pre + "o", (D, H * vdim)), norm=take(pre + "norm", (H * vdim,)))
+
+    def pack(self, prec):
+        w = self.w
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"]], 0).to("cuda", prec.dtype).contiguous()
+        self.w_o = w["o"].to("cuda", prec.dtype).contiguous()
+        self.norm = w["norm"].to("cuda", torch.float32)
+        self.decay_d = self.decay.to("cuda")
+
+    def __call__(self, h, b, store, li, prec):
+        H, dim, vdim = self.H, self.dim, self.vdim
+        proj = seq_ops.linear(h, self.w_in, prec.empty(b.T, self.w_in.shape[0]))
+        o = torch.empty(b.T, H * vdim, device="cuda", dtype=torch.float32)
+        seq_ops.linear_attn(proj, store.state[li], self.decay_d, o, b, H, dim, vdim)
+        att = prec.empty(b.T, H * vdim)
+        seq_ops.rmsnorm_gate(o, self.norm, proj[:, 2 * H * dim + H * vdim:], att, self.eps)
+        return seq_ops.linear(att, self.w_o, torch.empty(b.T, self.D, device="cuda", dtype=torch.float32))
+
+
+class GegluFeedForward:
+    def __init__(self, width, ff):
+        self.D, self.F = width, ff
+
+    def load(self, take, pre):
+        self.w = dict(gate=take(pre + "gate", (self.F, self.D)), up=take(pre + "up", (self.F, self.D)), down=take(pre + "down", (self.D, self.F)))
+
+    def pack(self, prec):
+        w, F, D = self.w, self.F, self.D
+        # bf16: the tcgen05 GEMM computes gelu(gate) * up in its epilogue from a [64 gate | 64 up] row-interleaved weight; F is
+        # padded to a multiple of 64 with zero rows (gelu(0) * 0 = 0) and zero columns of the down projection
+        self.fused = prec.dtype == torch.bfloat16 and D % 8 == 0
+        if self.fused:
+            Fp = (F + 63) // 64 * 64
+            gate = torch.zeros(Fp, D, device="cuda", dtype=torch.bfloat16)
+            up = torch.zeros_like(gate)
+            gate[:F], up[:F] = w["gate"].to("cuda", torch.bfloat16), w["up"].to("cuda", torch.bfloat16)
+            self.w_gu = torch.empty(2 * Fp, D, device="cuda", dtype=torch.bfloat16)
+            _lib.check(_lib.lib().pg_pack_gate_up(gate.data_ptr(), up.data_ptr(), self.w_gu.data_ptr(), Fp, D, _lib.stream()), "pg_pack_gate_up")
+            self.w_down = torch.zeros(D, Fp, device="cuda", dtype=torch.bfloat16)
+            self.w_down[:, :F] = w["down"].to("cuda", torch.bfloat16)
+            self.Fp = Fp
+            torch.cuda.synchronize()
+        else:
+            self.w_gu = torch.cat([w["gate"], w["up"]], 0).to("cuda", prec.dtype).contiguous()
+            self.w_down = w["down"].to("cuda", prec.dtype).contiguous()
+
+    def __call__(self, h, b, prec):
+        T = h.shape[0]
+        if self.fused:
+            mid = prec.empty(T, self.Fp)
+            _lib.gemm(h, self.w_gu, mid, mode=_lib.EPI_GEGLU, swap=1 if T <= 128 else 0)
+        else:
+            gu = seq_ops.linear(h, self.w_gu, prec.empty(T, 2 * self.F))
+            mid = prec.empty(T, self.F)
+            seq_ops.geglu(gu, mid)
+        return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class TokenSideInput:
+    """y = P (gelu_tanh(G x) * e), e = columns [index * dim, (index + 1) * dim) of the side table's row of the token."""
+
+    def __init__(self, width, dim, index):
+        self.D, self.n, self.index = width, dim, index
+
+    def load(self, take, pre):
+        self.w = dict(gate=take(pre + "gate", (self.n, self.D)), proj=take(pre + "proj", (self.D, self.n)))
+
+    def pack(self, prec):
+        n, D = self.n, self.D
+        self.n_pad = (n + 7) // 8 * 8  # TMA wants 16-byte pitches; the pad columns are zeros
+        self.w_gate = torch.zeros(self.n_pad, D, device="cuda", dtype=prec.dtype)
+        self.w_gate[:n] = self.w["gate"].to("cuda", prec.dtype)
+        self.w_proj = torch.zeros(D, self.n_pad, device="cuda", dtype=prec.dtype)
+        self.w_proj[:, :n] = self.w["proj"].to("cuda", prec.dtype)
+
+    def __call__(self, h, b, table, prec):
+        T = h.shape[0]
+        z = seq_ops.linear(h, self.w_gate, prec.empty(T, self.n_pad))
+        gz = prec.empty(T, self.n_pad)
+        seq_ops.side_gate(z, b.tokens, table, self.index * self.n, gz, self.n)
+        return seq_ops.linear(gz, self.w_proj, torch.empty(T, self.D, device="cuda", dtype=torch.float32))

@@ -1,0 +1,160 @@
+"""Host wrappers of the ragged-step kernels (csrc/seq_elementwise.cu, csrc/seq_mixers.cu) and the step's batch descriptor.
+
+`Precision` says in which type activations and matrix operands live: bf16 (tcgen05 GEMMs with fp32 accumulation wherever
+the shape allows TMA, the plain-FMA kernel otherwise) or fp32 (plain-FMA GEMMs only, no reduced-precision tensor mode).
+Norm statistics, attention scores and probabilities, recurrent states and the residual stream are fp32 in both.
+"""
+import dataclasses
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class Precision:
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("activation type must be torch.bfloat16 or torch.float32")
+        self.dtype = dtype
+        self.f32 = int(dtype == torch.float32)
+
+    def empty(self, *shape):
+        return torch.empty(*shape, device="cuda", dtype=self.dtype)
+
+
+@dataclasses.dataclass
+class StepBatch:
+    """One ragged step on the device.  Rows are tokens; entry e owns rows [row0[e], row0[e] + n[e])."""
+    T: int
+    E: int
+    max_n: int
+    tokens: torch.Tensor      # int32 [T]
+    pos: torch.Tensor         # int32 [T] position of the row inside its sequence
+    row_entry: torch.Tensor   # int32 [T]
+    row0: torch.Tensor        # int32 [E]
+    n: torch.Tensor           # int32 [E]
+    ctx: torch.Tensor         # int32 [E] tokens of the sequence already stored before this step
+    slot: torch.Tensor        # int32 [E] recurrent-state slot
+    page_table: torch.Tensor  # int32 [E, max_pages]
+    max_pages: int
+
+
+def make_step_batch(entries: Sequence[dict]) -> StepBatch:
+    """entries: dicts with tokens (list[int]), ctx (int), slot (int), pages (list[int]).  One host buffer, one copy."""
+    E = len(entries)
+    ns = [len(e["tokens"]) for e in entries]
+    T = sum(ns)
+    if E == 0 or min(ns) <= 0:
+        raise ValueError("a step needs at least one entry and every entry at least one token")
+    max_pages = max(1, max(len(e["pages"]) for e in entries))
+    buf = np.zeros(3 * T + 4 * E + E * max_pages, dtype=np.int32)
+    tokens, pos, row_entry = buf[:T], buf[T:2 * T], buf[2 * T:3 * T]
+    o = 3 * T
+    row0, n, ctx, slot = buf[o:o + E], buf[o + E:o + 2 * E], buf[o + 2 * E:o + 3 * E], buf[o + 3 * E:o + 4 * E]
+    pt = buf[o + 4 * E:].reshape(E, max_pages)
+    r = 0
+    for i, e in enumerate(entries):
+        k = ns[i]
+        if (e["ctx"] + k + 63) // 64 > len(e["pages"]):
+            raise ValueError("entry does not own enough pages for its new tokens")
+        tokens[r:r + k] = e["tokens"]
+        pos[r:r + k] = np.arange(e["ctx"], e["ctx"] + k)
+        row_entry[r:r + k] = i
+        row0[i], n[i], ctx[i], slot[i] = r, k, e["ctx"], e["slot"]
+        pt[i, :len(e["pages"])] = e["pages"]
+        r += k
+    dev = torch.from_numpy(buf).pin_memory().to("cuda", non_blocking=True)
+    o = 3 * T
+    return StepBatch(T=T, E=E, max_n=max(ns), tokens=dev[:T], pos=dev[T:2 * T], row_entry=dev[2 * T:3 * T], row0=dev[o:o + E],
+                     n=dev[o + E:o + 2 * E], ctx=dev[o + 2 * E:o + 3 * E], slot=dev[o + 3 * E:o + 4 * E],
+                     page_table=dev[o + 4 * E:].view(E, max_pages), max_pages=max_pages)
+
+
+def _aligned(t, n=16):
+    return t.data_ptr() % n == 0
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """out[t, f] = sum_k x[t, k] w[f, k].  x, w share a type (bf16 / fp32); out is bf16 or fp32.  bf16 operands go to the
+    tcgen05 kernel when TMA can describe them (16-byte pitches and bases), everything else to the plain-FMA kernel."""
+    T, K = x.shape
+    F = w.shape[0]
+    assert x.dtype == w.dtype and w.shape[1] == K and out.shape[0] == T and out.shape[1] == F
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and F % 8 == 0
+            and out.stride(0) % 8 == 0 and _aligned(x) and _aligned(w) and _aligned(out)):
+        return _lib.gemm(x, w, out, mode=_lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_BF16, swap=1 if T <= 128 else 0)
+    if x.dtype == torch.float32 and out.dtype != torch.float32:
+        raise ValueError("fp32 operands produce fp32 outputs")
+    _lib.check(_lib.lib().pg_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), T, F, K,
+                                       int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt")
+    return out
+
+
+def embed_rows(tokens, table, col0, D, scale):
+    out = torch.empty(tokens.numel(), D, device="cuda", dtype=torch.float32)
+    _lib.check(_lib.lib().pg_embed_rows(tokens.data_ptr(), table.data_ptr(), table.stride(0), int(col0), out.data_ptr(), tokens.numel(), D,
+                                        float(scale), int(table.dtype == torch.float32), _lib.stream()), "pg_embed_rows")
+    return out
+
+
+def group_rmsnorm_add(y, w, x, out_act, groups, eps):
+    """x += gnorm(y) * w (x fp32, in place; x None: bare norm); out_act (bf16 / fp32, may be None) gets a copy of the result."""
+    rows, D = y.shape
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and w.dtype == torch.float32 and w.numel() == D
+    assert x is None or (x.dtype == torch.float32 and x.is_contiguous() and x.shape == y.shape)
+    assert out_act is None or (out_act.is_contiguous() and out_act.shape == y.shape)
+    _lib.check(_lib.lib().pg_group_rmsnorm_add(y.data_ptr(), y.stride(0), w.data_ptr(), _lib.ptr(x), _lib.ptr(out_act), rows, D, int(groups),
+                                               float(eps), int(out_act is not None and out_act.dtype == torch.float32), _lib.stream()),
+               "pg_group_rmsnorm_add")
+
+
+def rmsnorm_gate(o, w, gate, out, eps):
+    rows, D = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == out.dtype and out.is_contiguous() and gate.stride(1) == 1
+    _lib.check(_lib.lib().pg_rmsnorm_gate(o.data_ptr(), w.data_ptr(), gate.data_ptr(), gate.stride(0), out.data_ptr(), rows, D, float(eps),
+                                          int(out.dtype == torch.float32), _lib.stream()), "pg_rmsnorm_gate")
+
+
+def geglu(gu, out):
+    rows, F = out.shape
+    assert gu.shape[1] == 2 * F and gu.dtype == out.dtype
+    _lib.check(_lib.lib().pg_geglu(gu.data_ptr(), gu.stride(0), out.data_ptr(), out.stride(0), rows, F, int(out.dtype == torch.float32),
+                                   _lib.stream()), "pg_geglu")
+
+
+def side_gate(z, tokens, table, col0, out, n):
+    rows, n_pad = out.shape
+    assert z.dtype == out.dtype == table.dtype
+    _lib.check(_lib.lib().pg_side_gate(z.data_ptr(), z.stride(0), tokens.data_ptr(), table.data_ptr(), table.stride(0), int(col0), out.data_ptr(),
+                                       out.stride(0), rows, int(n), n_pad, int(out.dtype == torch.float32), _lib.stream()), "pg_side_gate")
+
+
+def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_pages, H, G, dim, vdim, rot_dims, eps, page):
+    assert qkv.stride(1) == 1 and freq.dtype == torch.float64 and k_pages.dtype == qkv.dtype == q_out.dtype
+    _lib.check(_lib.lib().pg_attn_prepare(qkv.data_ptr(), qkv.stride(0), b.pos.data_ptr(), b.row_entry.data_ptr(), b.page_table.data_ptr(),
+                                          b.max_pages, page, freq.data_ptr(), q_norm.data_ptr(), k_norm.data_ptr(), q_out.data_ptr(),
+                                          k_pages.data_ptr(), v_pages.data_ptr(), b.T, H, G, dim, vdim, rot_dims, float(eps),
+                                          int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
+
+
+def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page):
+    _lib.check(_lib.lib().pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), 0 if gate is None else gate.stride(0),
+                                         out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(),
+                                         b.max_pages, page, b.E, b.max_n, H, G, dim, vdim, float(scale), float(softcap or 0.0),
+                                         int(q.dtype == torch.float32), _lib.stream()), "pg_attn_ragged")
+
+
+# a portion at least this long is advanced in 32-token blocks; shorter ones (decode above all) token by token
+LINEAR_ATTN_CHUNK_MIN = 8
+
+
+def linear_attn(qkv, state, decay, out, b: StepBatch, H, dim, vdim, chunked=None):
+    assert state.dtype == torch.float32 and out.dtype == torch.float32 and out.is_contiguous() and qkv.stride(1) == 1
+    if chunked is None:
+        chunked = b.max_n >= LINEAR_ATTN_CHUNK_MIN
+    fn = _lib.lib().pg_linear_attn_chunked if chunked else _lib.lib().pg_linear_attn_scan
+    _lib.check(fn(qkv.data_ptr(), qkv.stride(0), state.data_ptr(), decay.data_ptr(), out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(),
+                  b.ctx.data_ptr(), b.slot.data_ptr(), b.E, H, dim, vdim, int(qkv.dtype == torch.float32), _lib.stream()), "pg_linear_attn")

@@ -122,6 +122,79 @@ class SlotScheduler:
         return False
 
 
+@dataclasses.dataclass
+class TokenRequest:
+    """A text-only request of the ragged-step engine (engine.SequenceEngine)."""
+    rid: int
+    prompt: List[int]
+    max_new_tokens: int
+    fed: int = 0                                   # prompt tokens already run
+    tokens: List[int] = dataclasses.field(default_factory=list)
+    pages: int = 0                                 # pages set aside for it at admission (prompt + budget)
+
+
+class StepScheduler:
+    """Host-side planner of ragged steps (no tensors; CPU-testable): FIFO queue -> live requests (one sequence slot each and
+    enough KV pages for prompt + budget, set aside at admission so that a live request can always finish) -> per step, ONE
+    token of every decoding request plus prompt portions of the prefilling ones up to `step_tokens` rows.  Portions are cut
+    wherever the row budget ends; the model's arithmetic does not depend on the cut.  Stop rule as SlotScheduler: EOS is
+    appended, then the request stops; otherwise after max_new_tokens."""
+
+    def __init__(self, num_slots: int, num_pages: int, page: int = 64, step_tokens: int = 512, eos_token_id: Optional[int] = None):
+        if num_slots <= 0 or num_pages <= 0 or step_tokens <= 0:
+            raise ValueError("num_slots, num_pages and step_tokens must be positive")
+        self.num_slots, self.num_pages, self.page, self.step_tokens = int(num_slots), int(num_pages), int(page), int(step_tokens)
+        self.eos_token_id = eos_token_id
+        self.pages_out = 0
+        self.queue = collections.deque()
+        self.live: Dict[int, TokenRequest] = {}
+        self.finished: Dict[int, List[int]] = {}
+
+    def submit(self, req: TokenRequest):
+        need = (len(req.prompt) + req.max_new_tokens + self.page - 1) // self.page
+        if need > self.num_pages:
+            raise ValueError(f"request needs {need} pages, the pool has {self.num_pages}")
+        if not req.prompt or req.max_new_tokens < 1:
+            raise ValueError("a request needs a prompt and a budget of at least one token")
+        req.pages = need
+        self.queue.append(req)
+
+    def idle(self) -> bool:
+        return not self.queue and not self.live
+
+    def plan(self) -> List[Tuple[TokenRequest, List[int], bool]]:
+        """[(request, tokens to run this step, sample after them)] -- admits from the queue first (in order, no overtaking)."""
+        while self.queue and len(self.live) < self.num_slots and self.pages_out + self.queue[0].pages <= self.num_pages:
+            req = self.queue.popleft()
+            self.pages_out += req.pages
+            self.live[req.rid] = req
+        plan, budget = [], self.step_tokens
+        for req in self.live.values():              # decoding requests first: one row each
+            if req.fed == len(req.prompt) and budget > 0:
+                plan.append((req, [req.tokens[-1]], True))
+                budget -= 1
+        for req in self.live.values():
+            if req.fed < len(req.prompt) and budget > 0:
+                k = min(budget, len(req.prompt) - req.fed)
+                plan.append((req, req.prompt[req.fed:req.fed + k], req.fed + k == len(req.prompt)))
+                budget -= k
+        return plan
+
+    def advance(self, req: TokenRequest, ran: int, sampled: Optional[int]) -> bool:
+        """Books a step's outcome for one request; True when it finished (its slot and pages are free again)."""
+        if req.fed < len(req.prompt):
+            req.fed += ran
+        if sampled is None:
+            return False
+        req.tokens.append(int(sampled))
+        if len(req.tokens) >= req.max_new_tokens or (self.eos_token_id is not None and int(sampled) == self.eos_token_id):
+            self.finished[req.rid] = req.tokens
+            del self.live[req.rid]
+            self.pages_out -= req.pages
+            return True
+        return False
+
+
 class ContinuousBatcher:
     def __init__(self, model, num_slots: int, max_prompt_len: int, max_new_tokens: int, do_sample: bool = False,
                  temperature: float = 0.8, top_p: float = 0.9, eos_token_id: Optional[int] = None, seed: int = 0,

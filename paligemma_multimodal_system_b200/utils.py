@@ -51,6 +51,41 @@ def remap_hf_key(key: str) -> str:
     return key
 
 
+_ST_DTYPES = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32, "I64": torch.int64,
+              "F64": torch.float64, "U8": torch.uint8, "I8": torch.int8, "I16": torch.int16, "BOOL": torch.bool}
+
+
+def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
+    """name -> CPU tensor of one safetensors file, read directly: 8-byte little-endian header length, that many bytes of
+    JSON (name -> dtype, shape, data_offsets relative to the end of the header), then the data."""
+    import struct
+    with open(path, "rb") as f:
+        raw = f.read()
+    if len(raw) < 8:
+        raise ValueError(f"{path}: not a safetensors file")
+    (n,) = struct.unpack("<Q", raw[:8])
+    if 8 + n > len(raw):
+        raise ValueError(f"{path}: header length {n} exceeds the file")
+    meta = json.loads(raw[8:8 + n].decode("utf-8"))
+    data = memoryview(raw)[8 + n:]
+    out = {}
+    for name, m in meta.items():
+        if name == "__metadata__":
+            continue
+        dt = _ST_DTYPES.get(m["dtype"])
+        if dt is None:
+            raise ValueError(f"{path}: tensor {name} has unsupported dtype {m['dtype']}")
+        a, b = m["data_offsets"]
+        count = 1
+        for d in m["shape"]:
+            count *= int(d)
+        if b - a != count * torch.empty(0, dtype=dt).element_size() or b > len(data):
+            raise ValueError(f"{path}: tensor {name} has inconsistent offsets")
+        t = torch.frombuffer(bytearray(data[a:b]), dtype=dt) if count else torch.empty(0, dtype=dt)
+        out[name] = t.reshape([int(d) for d in m["shape"]])
+    return out
+
+
 def read_hf_checkpoint(model_path: str) -> Tuple[Dict[str, torch.Tensor], dict]:
     """Every tensor of every `*.safetensors` shard under reference-style keys (CPU), and the parsed config.json."""
     from safetensors import safe_open
