@@ -390,7 +390,24 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-serving", action="store_true", help="skip the continuous-batching sample (N = 1 only)")
     ap.add_argument("--no-configs", action="store_true", help="skip the cfg2 / cfg4 / cfg5 / strong-scaling measurements")
+    # --arch mapedra: the Mapedra decoder beside the Gemma decoder at equal layer sizes (paligemma_multimodal_system_b200/bench_seq.py);
+    # the default (paligemma) workload and its JSON contract are untouched by these flags
+    ap.add_argument("--arch", default="paligemma", choices=["paligemma", "mapedra"])
+    ap.add_argument("--width", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=64, choices=[64, 256], help="head sizes the Gemma attention kernels are built for")
+    ap.add_argument("--ff", type=int, default=8192)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--prefill-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=1024)
     args = ap.parse_args()
+    if args.arch == "mapedra":
+        from paligemma_multimodal_system_b200 import bench_seq
+        return bench_seq.run(args)
 
     from paligemma_multimodal_system_b200.random_init import make_inputs, paligemma_3b_config
     cfg = paligemma_3b_config(args.image_size)
