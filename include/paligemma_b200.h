@@ -317,10 +317,18 @@ int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* ro
 /* Causal attention of every entry's new rows over its cached keys / values (query head h reads k/v head h / (H / G)):
  * s = (q . k) * scale, s <- softcap * tanh(s / softcap) when softcap > 0, softmax over keys 0 .. position, times V; the
  * result is multiplied by sigmoid(gate[t, h * vdim + c]) when gate != NULL and written to out [rows, H * vdim].
- * page_table: int32 [entries, max_pages]; max_n = the largest entry_n (sizes the grid). */
+ * page_table: int32 [entries, max_pages]; max_n = the largest entry_n (sizes the grid).  skip_single != 0 leaves entries with
+ * entry_n == 1 to pg_attn_decode.
+ * pg_attn_decode handles ONLY entries with entry_n == 1 (decoded tokens): nsplit CTAs per (entry, k/v head) share the keys,
+ * every warp streams its own 32-key tiles from the pages; with nsplit > 1 the partial (max, sum, accumulator) triples go
+ * through `partial` (fp32 [entries, H, nsplit, vdim + 2]) and a merge launch. */
 int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                   int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream);
+                   int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
+                   void* stream);
+int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
+                   const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
+                   int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream);
 
 /* Decayed linear attention on qkv[t] = [q heads | k heads | v heads | ...] (q, k: H x dim, v: H x vdim; silu applied here):
  * per head S <- decay[h] * S + k v^T, out[t, h * vdim + :] = S^T q (fp32).  state: fp32 [slots, H, dim, vdim]; entry e

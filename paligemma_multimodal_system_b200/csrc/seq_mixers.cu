@@ -113,9 +113,10 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
                                                           const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
                                                           const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                           const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
-                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap) {
+                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single) {
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
   const int n = entry_n[e], ctx = entry_ctx[e], row0 = entry_row0[e];
+  if (skip_single && n == 1) return;
   const int rows = n * gsz;
   const int r0 = blockIdx.x * 32;
   if (r0 >= rows) return;
@@ -227,6 +228,243 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
         stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
       }
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention of single new tokens (decode rows: entries with n == 1).  CTA = (key split, k/v head, entry), 8 warps; every
+// warp walks its own 32-key tiles straight from the cache pages (lane <-> key for the scores, lane <-> value columns for
+// P V), no block-wide barrier inside the loop.  The warps' (max, sum, accumulator) triples are merged through shared memory;
+// with several key splits the CTA leaves its triple in `partial` and attn_decode_merge_kernel finishes the row.
+// Up to 4 query heads of the group per pass (the keys are re-read for more).
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename TA>
+__device__ __forceinline__ void ld8(const TA* p, float* v);
+template <>
+__device__ __forceinline__ void ld8<float>(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void ld8<bf16>(const bf16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// VC = ceil(vdim / 64).  VEC: 16-byte loads -- lane l reads key l's row for the scores; for P V the warp reads four keys per
+// instruction (lane = key l / 8 of the four, value columns 8 (l % 8) .. + 8 of every 64) and the four key groups are summed
+// by shuffles at the end.  All loads of a tile are independent, so a tile costs about one memory round trip.
+template <typename TA, int VC, bool VEC>
+__global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__ q, const TA* __restrict__ k_pages, const TA* __restrict__ v_pages,
+                                                          const TA* __restrict__ gate, long long ldg, TA* __restrict__ out, float* __restrict__ partial,
+                                                          const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
+                                                          const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
+                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap) {
+  constexpr int NO = VEC ? 8 * VC : 2 * VC;  // accumulator columns per lane
+  const int e = blockIdx.z, g = blockIdx.y, split = blockIdx.x, nsplit = gridDim.x, gsz = H / G;
+  if (entry_n[e] != 1) return;
+  const int ctx = entry_ctx[e];
+  const long long t = entry_row0[e];
+  const int dimp = (dim + 7) & ~7;
+  extern __shared__ __align__(16) float sm[];
+  float* Qs = sm;                       // [gsz][dimp]
+  float* Pw = Qs + gsz * dimp;          // [8][4][32]
+  float* Mg = Pw + 8 * 128;             // [8][4] max, [8][4] sum, then [8][4][vdim] accumulators
+  float* Lg = Mg + 32;
+  float* Og = Lg + 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kg = lane >> 3, l8 = lane & 7;
+  for (int i = threadIdx.x; i < gsz * dimp; i += 256) {
+    const int r = i / dimp, d = i % dimp;
+    Qs[i] = d < dim ? ldf(q, t * ((long long)H * dim) + (long long)(g * gsz + r) * dim + d) : 0.f;
+  }
+  __syncthreads();
+  const int* pt = page_table + (long long)e * max_pages;
+  const int ntiles = ctx / 32 + 1;  // keys 0 .. ctx
+  const long long krow = (long long)G * dim, vrow = (long long)G * vdim;
+  for (int rb = 0; rb < gsz; rb += 4) {
+    const int nr = min(4, gsz - rb);
+    float m[4], l[4], o[4][NO];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      m[i] = -INFINITY; l[i] = 0.f;
+#pragma unroll
+      for (int c = 0; c < NO; ++c) o[i][c] = 0.f;
+    }
+    for (int it = split * 8 + warp; it < ntiles; it += nsplit * 8) {
+      const int j = it * 32 + lane;
+      const bool vis = j <= ctx;
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      if (vis) {
+        const TA* kr = k_pages + ((long long)pt[j / page] * page + j % page) * krow + (long long)g * dim;
+        if (VEC) {
+#pragma unroll 4
+          for (int d = 0; d < dim; d += 8) {
+            float kv[8];
+            ld8(kr + d, kv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (i < nr) {
+                const float4 qa = *reinterpret_cast<const float4*>(Qs + (rb + i) * dimp + d), qb = *reinterpret_cast<const float4*>(Qs + (rb + i) * dimp + d + 4);
+                s[i] = fmaf(qa.x, kv[0], s[i]); s[i] = fmaf(qa.y, kv[1], s[i]); s[i] = fmaf(qa.z, kv[2], s[i]); s[i] = fmaf(qa.w, kv[3], s[i]);
+                s[i] = fmaf(qb.x, kv[4], s[i]); s[i] = fmaf(qb.y, kv[5], s[i]); s[i] = fmaf(qb.z, kv[6], s[i]); s[i] = fmaf(qb.w, kv[7], s[i]);
+              }
+          }
+        } else {
+          for (int d = 0; d < dim; ++d) {
+            const float kv = ldf(kr, d);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (i < nr) s[i] = fmaf(Qs[(rb + i) * dimp + d], kv, s[i]);
+          }
+        }
+      }
+      float* pw = Pw + warp * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float sc = s[i] * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+        sc = vis ? sc : -INFINITY;
+        const float mn = fmaxf(m[i], wmax(sc));  // key it * 32 <= ctx is always visible: mn is finite
+        const float pr = vis ? expf(sc - mn) : 0.f;
+        const float corr = expf(m[i] - mn);
+        l[i] = l[i] * corr + wsum(pr);
+        m[i] = mn;
+#pragma unroll
+        for (int c = 0; c < NO; ++c) o[i][c] *= corr;
+        pw[i * 32 + lane] = pr;
+      }
+      __syncwarp();
+      if (VEC) {
+        // a 32-key tile never straddles a page (the page size is a multiple of 32)
+        const TA* vt = v_pages + ((long long)pt[(it * 32) / page] * page + (it * 32) % page) * vrow + (long long)g * vdim;
+#pragma unroll
+        for (int jj0 = 0; jj0 < 32; jj0 += 4) {
+          const int jj = jj0 + kg;
+          if (it * 32 + jj <= ctx) {
+            float vv[8 * VC];
+#pragma unroll
+            for (int c = 0; c < VC; ++c) {
+              const int col = 8 * l8 + 64 * c;
+              if (col < vdim) ld8(vt + (long long)jj * vrow + col, vv + 8 * c);
+              else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) vv[8 * c + x] = 0.f;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float pj = pw[i * 32 + jj];
+#pragma unroll
+              for (int c = 0; c < 8 * VC; ++c) o[i][c] = fmaf(pj, vv[c], o[i][c]);
+            }
+          }
+        }
+      } else {
+        const int nk = min(32, ctx + 1 - it * 32);
+        for (int jj = 0; jj < nk; ++jj) {
+          const int key = it * 32 + jj;
+          const TA* vr = v_pages + ((long long)pt[key / page] * page + key % page) * vrow + (long long)g * vdim;
+          float vv[2 * VC];
+#pragma unroll
+          for (int c = 0; c < VC; ++c) {
+            const int col = 2 * lane + 64 * c;
+            vv[2 * c] = col < vdim ? ldf(vr, col) : 0.f;
+            vv[2 * c + 1] = col + 1 < vdim ? ldf(vr, col + 1) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float pj = pw[i * 32 + jj];
+#pragma unroll
+            for (int c = 0; c < 2 * VC; ++c) o[i][c] = fmaf(pj, vv[c], o[i][c]);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    if (VEC) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < NO; ++c) {
+          o[i][c] += __shfl_xor_sync(0xffffffffu, o[i][c], 8);
+          o[i][c] += __shfl_xor_sync(0xffffffffu, o[i][c], 16);
+        }
+    }
+    // merge the 8 warps
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (lane == 0) { Mg[warp * 4 + i] = m[i]; Lg[warp * 4 + i] = l[i]; }
+      if (VEC) {
+        if (kg == 0) {
+#pragma unroll
+          for (int c = 0; c < NO; ++c) {
+            const int col = 8 * l8 + 64 * (c / 8) + (c % 8);
+            if (col < vdim) Og[(warp * 4 + i) * vdim + col] = o[i][c];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NO; ++c) {
+          const int col = 2 * lane + 64 * (c / 2) + (c % 2);
+          if (col < vdim) Og[(warp * 4 + i) * vdim + col] = o[i][c];
+        }
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nr * vdim; idx += 256) {
+      const int i = idx / vdim, col = idx % vdim;
+      float M = -INFINITY;
+      for (int w = 0; w < 8; ++w) M = fmaxf(M, Mg[w * 4 + i]);
+      float acc = 0.f, ls = 0.f;
+      if (M > -INFINITY)
+        for (int w = 0; w < 8; ++w) {
+          const float f = expf(Mg[w * 4 + i] - M);
+          acc = fmaf(f, Og[(w * 4 + i) * vdim + col], acc);
+          ls = fmaf(f, Lg[w * 4 + i], ls);
+        }
+      const int head = g * gsz + rb + i;
+      if (nsplit == 1) {
+        float v = acc / ls;
+        if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (long long)head * vdim + col));
+        stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
+      } else {
+        float* pp = partial + (((long long)e * H + head) * nsplit + split) * (vdim + 2);
+        pp[2 + col] = acc;
+        if (col == 0) { pp[0] = M; pp[1] = ls; }
+      }
+    }
+  }
+}
+
+template <typename TA>
+__global__ void attn_decode_merge_kernel(const float* __restrict__ partial, const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
+                                         const int* __restrict__ entry_row0, const int* __restrict__ entry_n, int H, int vdim, int nsplit) {
+  const int e = blockIdx.y, head = blockIdx.x;
+  if (entry_n[e] != 1) return;
+  const long long t = entry_row0[e];
+  const float* pp = partial + ((long long)e * H + head) * nsplit * (vdim + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pp[s * (vdim + 2)]);
+  for (int col = threadIdx.x; col < vdim; col += blockDim.x) {
+    float acc = 0.f, ls = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = pp[s * (vdim + 2)];
+      if (ms > -INFINITY) {
+        const float f = expf(ms - M);
+        acc = fmaf(f, pp[s * (vdim + 2) + 2 + col], acc);
+        ls = fmaf(f, pp[s * (vdim + 2) + 1], ls);
+      }
+    }
+    float v = acc / ls;
+    if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (long long)head * vdim + col));
+    stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
   }
 }
 
@@ -424,7 +662,7 @@ extern "C" int pg_attn_prepare(const void* qkv, long long ld, const int* pos, co
 template <typename TA, int VC>
 static int launch_attn_ragged(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0,
                               const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int max_n, int H, int G,
-                              int dim, int vdim, float scale, float softcap, cudaStream_t st) {
+                              int dim, int vdim, float scale, float softcap, int skip_single, cudaStream_t st) {
   const int dimp = (dim + 3) & ~3;
   const size_t smem = ((size_t)32 * dimp + 32 * (dimp + 4) + 32 * vdim + 8 * 128) * sizeof(float);
   if (smem > 220 * 1024) return PG_ERR_ARG;
@@ -432,19 +670,19 @@ static int launch_attn_ragged(const void* q, const void* kp, const void* vp, con
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   dim3 grid((max_n * (H / G) + 31) / 32, G, entries);
   kern<<<grid, 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp), static_cast<const TA*>(gate), ldg,
-                                static_cast<TA*>(out), row0, n, ctx, pt, max_pages, page, H, G, dim, vdim, scale, softcap);
+                                static_cast<TA*>(out), row0, n, ctx, pt, max_pages, page, H, G, dim, vdim, scale, softcap, skip_single);
   PG_RET();
 }
 
 extern "C" int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                              int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream) {
+                              int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32, void* stream) {
   if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 256 || entries > 65535 || G > 65535)
     return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
 #define PG_ATTN(TA, VC) \
   return launch_attn_ragged<TA, VC>(q, k_pages, v_pages, gate, ldg, out, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, max_n, \
-                                    H, G, dim, vdim, scale, softcap, st)
+                                    H, G, dim, vdim, scale, softcap, skip_single, st)
   if (act_f32) {
     if (vdim <= 64) PG_ATTN(float, 2);
     if (vdim <= 128) PG_ATTN(float, 4);
@@ -509,4 +747,52 @@ extern "C" int pg_linear_attn_chunked(const void* qkv, long long ld, float* stat
     kern<<<grid, 256, smem, st>>>(static_cast<const bf16*>(qkv), ld, state, decay, out, entry_row0, entry_n, entry_ctx, entry_slot, H, dim, vdim, VB);
   }
   PG_RET();
+}
+
+template <typename TA, int VC, bool VEC>
+static int launch_attn_decode(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, float* partial,
+                              const int* row0, const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H,
+                              int G, int dim, int vdim, float scale, float softcap, cudaStream_t st) {
+  const int gsz = H / G, dimp = (dim + 7) & ~7;
+  const size_t smem = ((size_t)gsz * dimp + 8 * 128 + 64 + (size_t)32 * vdim) * sizeof(float);
+  if (smem > 200 * 1024) return PG_ERR_ARG;
+  auto kern = attn_decode_kernel<TA, VC, VEC>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+  kern<<<dim3(nsplit, G, entries), 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp),
+                                                     static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), partial, row0, n, ctx, pt, max_pages, page,
+                                                     H, G, dim, vdim, scale, softcap);
+  pg_count_launch(1);
+  if (nsplit > 1) {
+    attn_decode_merge_kernel<TA><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit);
+    pg_count_launch(1);
+  }
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+}
+
+extern "C" int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
+                              const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
+                              int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream) {
+  if (entries <= 0 || nsplit <= 0 || nsplit > 64 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 256 || entries > 65535 ||
+      G > 65535 || (nsplit > 1 && partial == nullptr))
+    return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  // 16-byte loads need every head's key / value row to start on an 8-element boundary and tiles that stay inside a page
+  const bool vec = (dim % 8 == 0) && (vdim % 8 == 0) && (page % 32 == 0) && vdim <= 128 && ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0);
+#define PG_ATTD(TA, VC, VEC) \
+  return launch_attn_decode<TA, VC, VEC>(q, k_pages, v_pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, \
+                                         entries, nsplit, H, G, dim, vdim, scale, softcap, st)
+  if (act_f32) {
+    if (vec && vdim <= 64) PG_ATTD(float, 1, true);
+    if (vec) PG_ATTD(float, 2, true);
+    if (vdim <= 64) PG_ATTD(float, 1, false);
+    if (vdim <= 128) PG_ATTD(float, 2, false);
+    PG_ATTD(float, 4, false);
+  }
+  if (vec && vdim <= 64) PG_ATTD(bf16, 1, true);
+  if (vec) PG_ATTD(bf16, 2, true);
+  if (vdim <= 64) PG_ATTD(bf16, 1, false);
+  if (vdim <= 128) PG_ATTD(bf16, 2, false);
+  PG_ATTD(bf16, 4, false);
+#undef PG_ATTD
 }

@@ -39,6 +39,8 @@ class StepBatch:
     slot: torch.Tensor        # int32 [E] recurrent-state slot
     page_table: torch.Tensor  # int32 [E, max_pages]
     max_pages: int
+    singles: int = 0          # entries with one new token (decode rows)
+    max_single_ctx: int = 0   # the longest context among them
 
 
 def make_step_batch(entries: Sequence[dict]) -> StepBatch:
@@ -69,7 +71,8 @@ def make_step_batch(entries: Sequence[dict]) -> StepBatch:
     o = 3 * T
     return StepBatch(T=T, E=E, max_n=max(ns), tokens=dev[:T], pos=dev[T:2 * T], row_entry=dev[2 * T:3 * T], row0=dev[o:o + E],
                      n=dev[o + E:o + 2 * E], ctx=dev[o + 2 * E:o + 3 * E], slot=dev[o + 3 * E:o + 4 * E],
-                     page_table=dev[o + 4 * E:].view(E, max_pages), max_pages=max_pages)
+                     page_table=dev[o + 4 * E:].view(E, max_pages), max_pages=max_pages, singles=sum(k == 1 for k in ns),
+                     max_single_ctx=max([e["ctx"] for e, k in zip(entries, ns) if k == 1], default=0))
 
 
 def _aligned(t, n=16):
@@ -140,11 +143,24 @@ def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_page
                                           int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
 
 
-def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page):
-    _lib.check(_lib.lib().pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), 0 if gate is None else gate.stride(0),
-                                         out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(),
-                                         b.max_pages, page, b.E, b.max_n, H, G, dim, vdim, float(scale), float(softcap or 0.0),
-                                         int(q.dtype == torch.float32), _lib.stream()), "pg_attn_ragged")
+def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True):
+    """Entries with several new rows go to the tiled kernel, entries with ONE new row (decoded tokens) to the key-split
+    kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation order."""
+    L, f32 = _lib.lib(), int(q.dtype == torch.float32)
+    ldg = 0 if gate is None else gate.stride(0)
+    singles = b.singles if decode_kernel else 0
+    if singles < b.E:
+        _lib.check(L.pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
+                                    b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
+                                    float(scale), float(softcap or 0.0), int(singles > 0), f32, _lib.stream()), "pg_attn_ragged")
+    if singles:
+        tiles = b.max_single_ctx // 32 + 1
+        # enough CTAs for two waves, but at least two 32-key tiles for every warp of a CTA
+        nsplit = max(1, min(-(-2 * _lib.num_sms() // (G * singles)), tiles // 16, 32))
+        partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
+        _lib.check(L.pg_attn_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial),
+                                    b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit,
+                                    H, G, dim, vdim, float(scale), float(softcap or 0.0), f32, _lib.stream()), "pg_attn_decode")
 
 
 # a portion at least this long is advanced in 32-token blocks; shorter ones (decode above all) token by token

@@ -85,7 +85,7 @@ def run_cut(engine, rid, tokens, cuts):
 def _one_entry(spec, T, dtype, ctx=0):
     from paligemma_multimodal_system_b200.cache import SequenceStore
     from paligemma_multimodal_system_b200.seq_ops import make_step_batch
-    store = SequenceStore([spec], 512, 2, dtype)
+    store = SequenceStore([spec], 2048, 2, dtype)
     store.admit("a")
     rec = store.reserve("a", ctx + T)
     return store, make_step_batch([dict(tokens=[0] * T, ctx=ctx, slot=rec.slot, pages=rec.pages)])
@@ -200,11 +200,12 @@ def test_feed_forward_and_side_input_alone():
 # ----------------------------------------------------------------------------------------------------------------------
 # attention over the paged cache with a key that stands out
 # ----------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("ctx,n", [(0, 200), (130, 70), (199, 1), (64, 1), (63, 2)])
-@pytest.mark.parametrize("needle", [0, 1, 63, 64, 65, 127, 128])
+@pytest.mark.parametrize("ctx,n", [(0, 200), (130, 70), (199, 1), (64, 1), (63, 2), (1100, 1), (1060, 40)])
+@pytest.mark.parametrize("needle", [0, 1, 63, 64, 65, 127, 128, 1023, 1024])
 def test_far_key_at_page_borders_is_found(ctx, n, needle):
-    """Among ~200 random keys ONE (at `needle`) is aligned with the last query and scaled up: the output of the last row must
-    be that key's value.  Run as a prompt portion (n > 1) and as a decoded token (n = 1), needle on both sides of page edges."""
+    """Among hundreds of random keys ONE (at `needle`) is aligned with the last query and scaled up: the output of the last row
+    must be that key's value.  Run as a prompt portion (n > 1) and as a decoded token (n = 1, long contexts split the keys over
+    several CTAs), needle on both sides of page edges."""
     from paligemma_multimodal_system_b200 import seq_ops
     H, G, dim, vdim, total = 2, 1, 32, 32, ctx + n
     needle = min(needle, total - 1)
