@@ -326,6 +326,13 @@ int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, cons
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                    int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
                    void* stream);
+/* pg_attn_ragged for bf16 activations on the tensor cores (mma.sync m16n8k16): S = Q K^T from the bf16 operands with fp32
+ * accumulation; the fp32 probabilities are cut into three bf16 terms each and P V runs as three passes over the bf16 values,
+ * so no probability is rounded to bf16.  Head sizes (dim, vdim) in {(32,32), (64,64), (128,128), (64,128), (128,64)}; anything
+ * else returns PG_ERR_ARG and belongs to pg_attn_ragged. */
+int pg_attn_ragged_mma(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
+                       const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
+                       int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, void* stream);
 int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                    int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream);

@@ -71,6 +71,7 @@ SIGNATURES = {
     "pg_side_gate": [p, i64, p, p, i64, i32, p, i64, i32, i32, i32, i32, p],
     "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, p],
     "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p],
+    "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, p],
     "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, p],
     "pg_linear_attn_scan": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_linear_attn_chunked": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],

@@ -78,26 +78,32 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
     const int n = (is_q || is_k) ? dim : vdim;
     const long long off = is_q ? (long long)vec * dim : is_k ? (long long)H * dim + (long long)(vec - H) * dim
                                                             : (long long)(H + G) * dim + (long long)(vec - H - G) * vdim;
+    // lane <-> pairs (2i, 2i+1): a rotation never needs another lane's element; an odd last element is a pair with a zero
     float ss = 0.f;
-    for (int d = lane; d < n; d += 32) { const float v = ldf(row, off + d); ss = fmaf(v, v, ss); }
+    for (int d = 2 * lane; d < n; d += 64) {
+      const float a = ldf(row, off + d), b2 = d + 1 < n ? ldf(row, off + d + 1) : 0.f;
+      ss = fmaf(a, a, fmaf(b2, b2, ss));
+    }
     ss = wsum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-    if (is_q || is_k) {
-      const float* w = is_q ? qn : kn;
-      TA* dst = is_q ? q_out + t * ((long long)H * dim) + (long long)vec * dim
-                     : k_pages + pg_row * ((long long)G * dim) + (long long)(vec - H) * dim;
-      for (int d = lane; d < n; d += 32) {
-        float a = ldf(row, off + d) * inv * w[d];
-        if (d < rot) {
-          const float b = ldf(row, off + (d ^ 1)) * inv * w[d ^ 1];
-          const float c = cs[d >> 1], s = cs[rot / 2 + (d >> 1)];
-          a = (d & 1) ? a * c + b * s : a * c - b * s;
+    const float* w = is_q ? qn : kn;
+    TA* dst = is_q   ? q_out + t * ((long long)H * dim) + (long long)vec * dim
+              : is_k ? k_pages + pg_row * ((long long)G * dim) + (long long)(vec - H) * dim
+                     : v_pages + pg_row * ((long long)G * vdim) + (long long)(vec - H - G) * vdim;
+    for (int d = 2 * lane; d < n; d += 64) {
+      const bool two = d + 1 < n;
+      float a = ldf(row, off + d) * inv, b2 = two ? ldf(row, off + d + 1) * inv : 0.f;
+      if (is_q || is_k) {
+        a *= w[d];
+        if (two) b2 *= w[d + 1];
+        if (d < rot) {  // rot is even: the pair is rotated as a whole
+          const float c = cs[d >> 1], sn = cs[rot / 2 + (d >> 1)];
+          const float ra = a * c - b2 * sn, rb = b2 * c + a * sn;
+          a = ra; b2 = rb;
         }
-        stf(dst, d, a);
       }
-    } else {
-      TA* dst = v_pages + pg_row * ((long long)G * vdim) + (long long)(vec - H - G) * vdim;
-      for (int d = lane; d < n; d += 32) stf(dst, d, ldf(row, off + d) * inv);
+      stf(dst, d, a);
+      if (two) stf(dst, d + 1, b2);
     }
   }
 }

@@ -143,13 +143,23 @@ def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_page
                                           int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
 
 
-def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True):
-    """Entries with several new rows go to the tiled kernel, entries with ONE new row (decoded tokens) to the key-split
-    kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation order."""
+# head sizes (dim, vdim) the tensor-core attention kernel is instantiated for
+MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64)}
+
+
+def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True):
+    """Entries with several new rows go to a tiled kernel -- on the tensor cores for bf16 activations and the usual head
+    sizes (fp32 probabilities as three bf16 terms), plain fp32 FMAs otherwise -- and entries with ONE new row (decoded tokens)
+    to the key-split kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation
+    order."""
     L, f32 = _lib.lib(), int(q.dtype == torch.float32)
     ldg = 0 if gate is None else gate.stride(0)
     singles = b.singles if decode_kernel else 0
-    if singles < b.E:
+    if singles < b.E and tensor_cores and not f32 and (dim, vdim) in MMA_HEAD_SIZES and ldg % 2 == 0 and (gate is None or gate.data_ptr() % 4 == 0):
+        _lib.check(L.pg_attn_ragged_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
+                                        b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
+                                        float(scale), float(softcap or 0.0), int(singles > 0), _lib.stream()), "pg_attn_ragged_mma")
+    elif singles < b.E:
         _lib.check(L.pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
                                     b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
                                     float(scale), float(softcap or 0.0), int(singles > 0), f32, _lib.stream()), "pg_attn_ragged")

@@ -231,6 +231,44 @@ def test_far_key_at_page_borders_is_found(ctx, n, needle):
     assert (out.cpu().view(n, H, vdim)[-1, 0] - v[needle]).abs().max() < 1e-3  # the needle dominates
 
 
+@pytest.mark.parametrize("dim,vdim,H,G", [(64, 64, 6, 2), (32, 32, 2, 2), (128, 128, 2, 1), (64, 128, 4, 1), (128, 64, 3, 3)])
+@pytest.mark.parametrize("ctx,n", [(0, 150), (70, 61), (129, 2)])
+def test_tensor_core_attention_keeps_fp32_probabilities(dim, vdim, H, G, ctx, n):
+    """bf16 q / k / v through the tensor-core kernel against fp64 softmax attention of the same bf16 values: the error must be
+    at the level of the bf16 OUTPUT rounding only (a bf16-rounded probability matrix would sit ten times higher on the
+    flat rows this test makes), for every instantiated head size, with soft cap, gate, grouped heads and a cached context."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    total = ctx + n
+    g = torch.Generator().manual_seed(dim + n)
+    store, b = _one_entry(("kv", G * dim, G * vdim), n, torch.bfloat16, ctx=ctx)
+    k = (torch.randn(total, G, dim, generator=g) * 0.05).bfloat16()   # flat scores: hundreds of keys share the mass
+    v = torch.randn(total, G, vdim, generator=g).bfloat16()
+    q = torch.randn(n, H, dim, generator=g).bfloat16()
+    gate = torch.randn(n, H * vdim, generator=g).bfloat16()
+    pages = b.page_table[0].tolist()
+    for j in range(total):
+        store.k_pages[0][pages[j // 64], j % 64] = k[j].reshape(-1).cuda()
+        store.v_pages[0][pages[j // 64], j % 64] = v[j].reshape(-1).cuda()
+    outs = []
+    for tc in (True, False):
+        out = torch.empty(n, H * vdim, device="cuda", dtype=torch.bfloat16)
+        seq_ops.attn_ragged(q.reshape(n, H * dim).cuda().contiguous(), store.k_pages[0], store.v_pages[0], gate.cuda(), out, b, H, G, dim, vdim,
+                            0.3, 5.0, 64, decode_kernel=False, tensor_cores=tc)
+        outs.append(out.float().cpu())
+    ref = torch.zeros(n, H, vdim, dtype=torch.float64)
+    for i in range(n):
+        for h in range(H):
+            kv = h // (H // G)
+            s = (k[: ctx + i + 1, kv].double() @ q[i, h].double()) * 0.3
+            s = 5.0 * torch.tanh(s / 5.0)
+            ref[i, h] = torch.softmax(s, 0) @ v[: ctx + i + 1, kv].double()
+    ref = (ref.reshape(n, H * vdim) * torch.sigmoid(gate.double())).float()
+    for out in outs:
+        assert torch.allclose(out, ref, atol=4e-3, rtol=1e-2)
+    # before the final rounding both kernels carry fp32 probabilities: they agree to one bf16 ulp nearly everywhere
+    assert float((outs[0] - outs[1]).abs().max()) <= 2 ** -7 * float(ref.abs().max())
+
+
 def test_causal_edge_key_just_outside_is_not_seen():
     """A huge key one position AFTER a query must leave that query's output untouched, and one AT the query must take it over."""
     from paligemma_multimodal_system_b200 import seq_ops
