@@ -56,10 +56,37 @@ def test_inference(model: PaliGemmaForConditionalGeneration, processor, device: 
     return row
 
 
+def generate_token_ids(model_path: str, prompt_ids, max_tokens_to_generate: int, temperature: float, top_p: float, do_sample: bool,
+                       dtype: str = "bfloat16", max_tokens: int = 0, slots: int = 4, eos_token_id: int = None):
+    """Text-only checkpoints of the registry (config.json `architecture`, e.g. Mapedra) carry no tokenizer: prompts are lists of
+    token ids (several prompts separated by ';'), served by the ragged-step engine; prints and returns the new ids per prompt."""
+    from .engine import SequenceEngine
+    from .registry import load_model
+    prompts = [[int(t) for t in part.replace(",", " ").split()] for part in str(prompt_ids).split(";") if part.strip()]
+    model = load_model(model_path, dtype=getattr(torch, dtype))
+    need = sum((len(p) + max_tokens_to_generate + 63) // 64 * 64 for p in prompts[:slots])
+    engine = SequenceEngine(model, max(max_tokens, need), slots)
+    out = engine.generate(prompts, max_tokens_to_generate, do_sample=do_sample, temperature=temperature, top_p=top_p, eos_token_id=eos_token_id)
+    for p, o in zip(prompts, out):
+        print(" ".join(map(str, p)), "->", " ".join(map(str, o)))
+    return out
+
+
 def main(model_path: str = None, prompt: str = None, image_file_path: str = None, max_tokens_to_generate: int = 100,
-         temperature: float = 0.8, top_p: float = 0.9, do_sample: bool = False, only_cpu: bool = False):
+         temperature: float = 0.8, top_p: float = 0.9, do_sample: bool = False, only_cpu: bool = False, prompt_ids: str = None,
+         dtype: str = "bfloat16", max_tokens: int = 0, slots: int = 4, eos_token_id: int = None):
     if only_cpu:
         raise RuntimeError("this build has no CPU path: it needs a B200 (sm_100a)")
+    import json
+    import os
+    from .registry import architecture_of
+    with open(os.path.join(model_path, "config.json")) as fh:
+        arch = architecture_of(json.load(fh))
+    if arch.lower() not in ("paligemma", "paligemmaforconditionalgeneration"):
+        if prompt_ids is None:
+            raise SystemExit(f"{arch} is a text-only model without a tokenizer: pass --prompt_ids \"1 2 3\"")
+        return generate_token_ids(model_path, prompt_ids, max_tokens_to_generate, temperature, top_p, do_sample, dtype, max_tokens, slots,
+                                  eos_token_id)
     from .processing_paligemma import PaliGemmaProcessor
     from .utils import load_hf_model
     device = "cuda"
@@ -89,4 +116,9 @@ if __name__ == "__main__":
     ap.add_argument("--top_p", type=float, default=0.9)
     ap.add_argument("--do_sample", type=_str2bool, default=False)
     ap.add_argument("--only_cpu", type=_str2bool, default=False)
+    ap.add_argument("--prompt_ids", help="text-only models: token ids of the prompt(s), e.g. \"5 17 3; 8 9\"")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="text-only models: activation / matrix type")
+    ap.add_argument("--max_tokens", type=int, default=0, help="text-only models: tokens the KV page pool holds (0 = what the prompts need)")
+    ap.add_argument("--slots", type=int, default=4, help="text-only models: requests served at the same time")
+    ap.add_argument("--eos_token_id", type=int, default=None)
     main(**vars(ap.parse_args()))
