@@ -15,16 +15,20 @@ import torch
 
 from . import _lib
 from .cache import SequenceStore
-from .seq_ops import make_step_batch
+from .seq_ops import StaticDecodeBatch, make_step_batch
 from .serving import StepScheduler, TokenRequest
 
 
 class SequenceEngine:
-    def __init__(self, model, max_tokens: int, num_slots: int = 4):
+    def __init__(self, model, max_tokens: int, num_slots: int = 4, use_cuda_graph: bool = True):
         _lib.require_device()
         self.model = model
         self.store = SequenceStore(model.cache_layout(), max_tokens, num_slots, model.prec.dtype)
         self._step_no = torch.zeros(1, device="cuda", dtype=torch.int32)
+        # decode steps (every entry one token) replay a CUDA graph per (entries, page-table width, context bound); the second
+        # step of a geometry captures it, the first ran eagerly (lazy kernel attributes are set by then)
+        self.use_cuda_graph = use_cuda_graph
+        self._decode_graphs = {}
 
     @torch.no_grad()
     def step(self, entries: Sequence[Tuple[object, Sequence[int], Sequence[int]]], end: Sequence[object] = (), trace=None):
@@ -52,7 +56,11 @@ class SequenceEngine:
                 want.append(row + int(k))
             row += len(toks)
         logits = None
-        if batch:
+        if batch and trace is None and self.use_cuda_graph and all(len(e["tokens"]) == 1 for e in batch):
+            logits = self._decode_step(batch, want)
+            for (rid, toks, _w) in entries:
+                store.commit(rid, len(toks))
+        elif batch:
             b = make_step_batch(batch)
             rows = torch.tensor(want, dtype=torch.int64).to("cuda", non_blocking=True) if want else None
             logits = self.model.step(b, store, rows, trace=trace)
@@ -62,6 +70,39 @@ class SequenceEngine:
             if rid in store.live:
                 store.release(rid)
         return logits
+
+    def _decode_step(self, batch, want):
+        """A step of single-token entries through a captured graph (eagerly the first time a geometry is seen)."""
+        E = len(batch)
+        pages = max(len(e["pages"]) for e in batch)
+        pages_cap = 4
+        while pages_cap < pages:
+            pages_cap *= 2
+        ctx_cap = pages_cap * self.store.page  # every context of this page-table width; fixes the key split of the attention
+        key = (E, pages_cap)
+        slot = self._decode_graphs.get(key)
+        if slot is None:
+            slot = self._decode_graphs[key] = dict(static=StaticDecodeBatch(E, pages_cap, ctx_cap), graph=None, logits=None, seen=0)
+        st = slot["static"]
+        st.fill(batch)
+        slot["seen"] += 1
+        if slot["graph"] is None and slot["seen"] >= 2:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    slot["logits"] = self.model.step(st.batch, self.store, st.rows)
+            torch.cuda.current_stream().wait_stream(side)
+            slot["graph"] = g
+        if slot["graph"] is not None:
+            slot["graph"].replay()
+            full = slot["logits"]
+        else:
+            full = self.model.step(st.batch, self.store, st.rows)
+        if not want:
+            return None
+        return full.index_select(0, torch.tensor(want, dtype=torch.int64).to("cuda", non_blocking=True))
 
     def release(self, rid):
         self.store.release(rid)

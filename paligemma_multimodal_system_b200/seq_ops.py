@@ -75,6 +75,39 @@ def make_step_batch(entries: Sequence[dict]) -> StepBatch:
                      max_single_ctx=max([e["ctx"] for e, k in zip(entries, ns) if k == 1], default=0))
 
 
+class StaticDecodeBatch:
+    """Fixed-address StepBatch for steps of E single-token entries (a decode step), so that the step can be captured once in a
+    CUDA graph and replayed: `fill` rewrites the pinned host image and copies it over the device buffer in stream order.
+    `pages_cap` is the page-table width the graph was captured with; `ctx_cap` the context bound that fixed its key split."""
+
+    def __init__(self, E: int, pages_cap: int, ctx_cap: int):
+        self.E, self.pages_cap, self.ctx_cap = E, pages_cap, ctx_cap
+        n = 7 * E + E * pages_cap
+        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(n, dtype=torch.int32, device="cuda")
+        d = self.dev
+        self.batch = StepBatch(T=E, E=E, max_n=1, tokens=d[:E], pos=d[E:2 * E], row_entry=d[2 * E:3 * E], row0=d[3 * E:4 * E], n=d[4 * E:5 * E],
+                               ctx=d[5 * E:6 * E], slot=d[6 * E:7 * E], page_table=d[7 * E:].view(E, pages_cap), max_pages=pages_cap, singles=E,
+                               max_single_ctx=ctx_cap)
+        self.rows = torch.arange(E, device="cuda", dtype=torch.int64)
+        self._copied = None
+
+    def fill(self, entries: Sequence[dict]):
+        E, h = self.E, self.host.numpy()
+        assert len(entries) == E
+        if self._copied is not None:
+            self._copied.synchronize()  # the previous image must have left the pinned buffer before it is rewritten
+        h[7 * E:] = 0
+        pt = h[7 * E:].reshape(E, self.pages_cap)
+        for i, e in enumerate(entries):
+            assert len(e["tokens"]) == 1 and len(e["pages"]) <= self.pages_cap and e["ctx"] <= self.ctx_cap
+            h[i], h[E + i], h[2 * E + i], h[3 * E + i], h[4 * E + i], h[5 * E + i], h[6 * E + i] = e["tokens"][0], e["ctx"], i, i, 1, e["ctx"], e["slot"]
+            pt[i, :len(e["pages"])] = e["pages"]
+        self.dev.copy_(self.host, non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+
+
 def _aligned(t, n=16):
     return t.data_ptr() % n == 0
 
@@ -88,6 +121,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and F % 8 == 0
             and out.stride(0) % 8 == 0 and _aligned(x) and _aligned(w) and _aligned(out)):
+        if T <= 128 and out.dtype == torch.float32:
+            # few rows, few 128-feature tiles (output and down projections): split K over CTAs so that the whole GPU streams the
+            # weights; the fp32 partials are red.add-ed into the zeroed output (as the framework's other decode GEMMs do)
+            tiles, kb = (F + 127) // 128, (K + 63) // 64
+            split = max(1, min(kb // 4, (2 * _lib.num_sms()) // tiles))
+            if split > 1:
+                out.zero_()
+                return _lib.gemm(x, w, out, mode=_lib.EPI_ATOMIC_F32, swap=1, split_k=split)
         return _lib.gemm(x, w, out, mode=_lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_BF16, swap=1 if T <= 128 else 0)
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise ValueError("fp32 operands produce fp32 outputs")
