@@ -301,8 +301,8 @@ int pg_rmsnorm_gate(const float* o, const float* w, const void* gate, long long 
 int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int act_f32, void* stream);
 
 /* out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], col0 + j] for j < n, 0 for n <= j < n_pad (per-token side input: a
- * gate projection of the residual times the token's own low-dimensional embedding slice). */
-int pg_side_gate(const void* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
+ * gate projection of the residual, fp32, times the token's own low-dimensional embedding slice). */
+int pg_side_gate(const float* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
                  long long ldo, int rows, int n, int n_pad, int act_f32, void* stream);
 
 /* Softmax-attention front end on the fused projection rows qkv[t] = [q heads | k heads | v heads | ...] (pitch ld):

@@ -100,29 +100,75 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TI* __re
 
 // Grouped RMS norm of y (fp32) times w, optionally added to the fp32 residual row x (in place); the result (the new residual,
 // or the bare norm when x == NULL) is also written in the activation type when out_act != NULL.  One CTA per row; the
-// row is cut into `groups` equal consecutive parts with their own mean square.
-template <typename TO>
+// row is cut into `groups` equal consecutive parts with their own mean square.  The 8 warps share the groups (8 / groups warps
+// per group when that divides, else warp w takes groups w, w + 8, ...), one block barrier, then one pass that re-reads y from L1.
+// VEC: float4 accesses (group size a multiple of 4, 16-byte aligned rows).
+__device__ __forceinline__ void st_act4(float* p, long long i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void st_act4(bf16* p, long long i, float4 v) {
+  uint2 u;
+  u.x = pg::pack_bf16(v.x, v.y);
+  u.y = pg::pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(p + i) = u;
+}
+
+template <typename TO, bool VEC>
 __global__ void __launch_bounds__(256) group_rmsnorm_add_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ w,
                                                                 float* __restrict__ x, TO* __restrict__ out_act, int D, int groups, float eps) {
-  extern __shared__ float sm[];  // D values + 32 + groups
-  float* row = sm;
-  float* red = sm + D;
-  float* inv = red + 32;
+  extern __shared__ float sm[];  // 8 partial sums, then 1 / rms of every group
+  float* red = sm;
+  float* inv = sm + 8;
   const long long t = blockIdx.x;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) row[d] = y[t * ldy + d];
-  __syncthreads();
+  const float* yr = y + t * ldy;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gs = D / groups;
-  for (int g = 0; g < groups; ++g) {
+  const int wpg = (groups <= 8 && 8 % groups == 0) ? 8 / groups : 1;
+  if (wpg > 1) {
+    const int g = warp / wpg, part = warp % wpg;
     float s = 0.f;
-    for (int d = threadIdx.x; d < gs; d += blockDim.x) { const float v = row[g * gs + d]; s = fmaf(v, v, s); }
-    s = block_sum(s, red);
-    if (threadIdx.x == 0) inv[g] = 1.0f / sqrtf(s / (float)gs + eps);
+    if (VEC) {
+      const float4* y4 = reinterpret_cast<const float4*>(yr + (long long)g * gs);
+      for (int i = part * 32 + lane; i < gs / 4; i += wpg * 32) { const float4 v = y4[i]; s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s)))); }
+    } else {
+      for (int i = part * 32 + lane; i < gs; i += wpg * 32) { const float v = yr[(long long)g * gs + i]; s = fmaf(v, v, s); }
+    }
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;
+    __syncthreads();
+    if (threadIdx.x < groups) {
+      float tot = 0.f;
+      for (int p = 0; p < wpg; ++p) tot += red[threadIdx.x * wpg + p];
+      inv[threadIdx.x] = 1.0f / sqrtf(tot / (float)gs + eps);
+    }
+  } else {
+    for (int g = warp; g < groups; g += 8) {
+      float s = 0.f;
+      for (int i = lane; i < gs; i += 32) { const float v = yr[(long long)g * gs + i]; s = fmaf(v, v, s); }
+      s = warp_sum(s);
+      if (lane == 0) inv[g] = 1.0f / sqrtf(s / (float)gs + eps);
+    }
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float v = row[d] * inv[d / gs] * w[d];
-    if (x != nullptr) { v += x[t * D + d]; x[t * D + d] = v; }
-    if (out_act != nullptr) st_f(out_act, t * D + d, v);
+  if (VEC) {
+    const float4* y4 = reinterpret_cast<const float4*>(yr);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    for (int i = threadIdx.x; i < D / 4; i += 256) {
+      const float4 v = y4[i], ww = w4[i];
+      const float iv = inv[(i * 4) / gs];
+      float4 r = make_float4(v.x * iv * ww.x, v.y * iv * ww.y, v.z * iv * ww.z, v.w * iv * ww.w);
+      if (x != nullptr) {
+        float4* xp = reinterpret_cast<float4*>(x + t * D) + i;
+        const float4 xv = *xp;
+        r.x += xv.x; r.y += xv.y; r.z += xv.z; r.w += xv.w;
+        *xp = r;
+      }
+      if (out_act != nullptr) st_act4(out_act, t * D + 4LL * i, r);
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += 256) {
+      float v = yr[d] * inv[d / gs] * w[d];
+      if (x != nullptr) { v += x[t * D + d]; x[t * D + d] = v; }
+      if (out_act != nullptr) st_f(out_act, t * D + d, v);
+    }
   }
 }
 
@@ -152,16 +198,16 @@ __global__ void geglu_kernel(const TA* __restrict__ gu, long long ldgu, TA* __re
   st_f(out, t * ldo + f, pg::gelu_tanh(ld_f(gu, t * ldgu + f)) * ld_f(gu, t * ldgu + F + f));
 }
 
-// out[t, j] = gelu_tanh(z[t, j]) * table[token[t], col0 + j]  for j < n, zero for n <= j < n_pad
+// out[t, j] = gelu_tanh(z[t, j]) * table[token[t], col0 + j]  for j < n, zero for n <= j < n_pad   (z fp32)
 template <typename TA>
-__global__ void side_gate_kernel(const TA* __restrict__ z, long long ldz, const int* __restrict__ tokens, const TA* __restrict__ table, long long ldt,
+__global__ void side_gate_kernel(const float* __restrict__ z, long long ldz, const int* __restrict__ tokens, const TA* __restrict__ table, long long ldt,
                                  int col0, TA* __restrict__ out, long long ldo, int n, int n_pad, long long total) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / n_pad;
   const int j = (int)(i % n_pad);
   float v = 0.f;
-  if (j < n) v = pg::gelu_tanh(ld_f(z, t * ldz + j)) * ld_f(table, (long long)tokens[t] * ldt + col0 + j);
+  if (j < n) v = pg::gelu_tanh(z[t * ldz + j]) * ld_f(table, (long long)tokens[t] * ldt + col0 + j);
   st_f(out, t * ldo + j, v);
 }
 
@@ -196,16 +242,17 @@ extern "C" int pg_embed_rows(const int* tokens, const void* table, long long ld,
 
 extern "C" int pg_group_rmsnorm_add(const float* y, long long ldy, const float* w, float* x, void* out_act, int rows, int D, int groups,
                                     float eps, int out_f32, void* stream) {
-  if (rows <= 0 || D <= 0 || groups <= 0 || (D % groups) != 0 || D > 32768) return PG_ERR_ARG;
-  const size_t smem = (D + 32 + groups) * sizeof(float);
-  if (smem > 200 * 1024) return PG_ERR_ARG;
+  if (rows <= 0 || D <= 0 || groups <= 0 || (D % groups) != 0 || groups > 4096) return PG_ERR_ARG;
+  const size_t smem = (8 + groups) * sizeof(float);
   cudaStream_t st = PG_ST(stream);
+  const bool vec = ((D / groups) % 4 == 0) && (ldy % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out_act)) & 15) == 0;
   if (out_f32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(group_rmsnorm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    group_rmsnorm_add_kernel<float><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<float*>(out_act), D, groups, eps);
+    if (vec) group_rmsnorm_add_kernel<float, true><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<float*>(out_act), D, groups, eps);
+    else group_rmsnorm_add_kernel<float, false><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<float*>(out_act), D, groups, eps);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(group_rmsnorm_add_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    group_rmsnorm_add_kernel<bf16><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<bf16*>(out_act), D, groups, eps);
+    if (vec) group_rmsnorm_add_kernel<bf16, true><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<bf16*>(out_act), D, groups, eps);
+    else group_rmsnorm_add_kernel<bf16, false><<<rows, 256, smem, st>>>(y, ldy, w, x, static_cast<bf16*>(out_act), D, groups, eps);
   }
   PG_RET();
 }
@@ -231,16 +278,16 @@ extern "C" int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo
   PG_RET();
 }
 
-extern "C" int pg_side_gate(const void* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
+extern "C" int pg_side_gate(const float* z, long long ldz, const int* tokens, const void* table, long long ldt, int col0, void* out,
                             long long ldo, int rows, int n, int n_pad, int act_f32, void* stream) {
   if (rows <= 0 || n <= 0 || n_pad < n) return PG_ERR_ARG;
   const long long total = (long long)rows * n_pad;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (act_f32)
-    side_gate_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(z), ldz, tokens, static_cast<const float*>(table), ldt, col0,
+    side_gate_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(z, ldz, tokens, static_cast<const float*>(table), ldt, col0,
                                                               static_cast<float*>(out), ldo, n, n_pad, total);
   else
-    side_gate_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(z), ldz, tokens, static_cast<const bf16*>(table), ldt, col0,
+    side_gate_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(z, ldz, tokens, static_cast<const bf16*>(table), ldt, col0,
                                                              static_cast<bf16*>(out), ldo, n, n_pad, total);
   PG_RET();
 }

@@ -543,101 +543,166 @@ __global__ void __launch_bounds__(256) linear_attn_scan_kernel(const TA* __restr
 // CTA = (value-column block, head, entry); the state block [dim][VB] lives in shared memory for the whole entry.
 // Thread = value column x row group for the outputs, value column x key-dimension slice for the state update.
 // ---------------------------------------------------------------------------------------------------------------------
-template <typename TA>
+// VEC: the block's q / k / v rows are fetched with 16-byte loads ONE BLOCK AHEAD into registers (<= 2 + 2 + 1 loads per thread:
+// dim <= 128), so the memory round trip of block b + 1 hides behind the arithmetic of block b.
+template <typename TA, bool VEC, int VB>
 __global__ void __launch_bounds__(256) linear_attn_chunked_kernel(const TA* __restrict__ qkv, long long ld, float* __restrict__ state,
                                                                   const float* __restrict__ decay, float* __restrict__ out,
                                                                   const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                                   const int* __restrict__ entry_ctx, const int* __restrict__ entry_slot, int H,
-                                                                  int dim, int vdim, int VB) {
+                                                                  int dim, int vdim) {
   constexpr int C = 32;
   const int e = blockIdx.z, h = blockIdx.y, vb = blockIdx.x;
   const int n = entry_n[e], row0 = entry_row0[e];
-  const int ngrp = 256 / VB, rpt = C / ngrp;  // row groups; rows per thread (<= 8 because VB <= 64)
-  const int vl = threadIdx.x % VB, grp = threadIdx.x / VB;
+  constexpr int ngrp = 256 / VB, rpt = C / ngrp;  // row groups; rows per thread (8 for 64 value columns per CTA)
+  const int vl = threadIdx.x % VB, grp = threadIdx.x / VB;  // a warp lies inside one group: its row / key operands are broadcasts
   const int v = vb * VB + vl;
   const bool v_ok = v < vdim;
-  const int kd = dim + 1;
-  extern __shared__ float sm[];
+  const int dim4 = (dim + 3) & ~3, kd = dim4 + 4;  // padded key dimensions are zeros; rows stay 16-byte aligned
+  extern __shared__ __align__(16) float sm[];
   float* Qs = sm;                 // [C][kd]
   float* Ks = Qs + C * kd;        // [C][kd]
   float* Vs = Ks + C * kd;        // [C][VB]
   float* As = Vs + C * VB;        // [C][C]
-  float* Ss = As + C * C;         // [dim][VB]
-  float* ap = Ss + dim * VB;      // a^0 .. a^C
+  float* Ss = As + C * C;         // [dim4][VB]
+  float* ap = Ss + dim4 * VB;     // a^0 .. a^C
   float* st = state + (((long long)entry_slot[e] * H + h) * dim) * vdim;
   const bool fresh = entry_ctx[e] == 0;
-  for (int i = threadIdx.x; i < dim * VB; i += 256) {
+  for (int i = threadIdx.x; i < dim4 * VB; i += 256) {
     const int d = i / VB, c = vb * VB + i % VB;
-    Ss[i] = (!fresh && c < vdim) ? st[(long long)d * vdim + c] : 0.f;
+    Ss[i] = (!fresh && d < dim && c < vdim) ? st[(long long)d * vdim + c] : 0.f;
   }
   const double a = (double)decay[h];
   for (int i = threadIdx.x; i <= C; i += 256) ap[i] = (float)pow(a, (double)i);
   const long long qo = (long long)h * dim, ko = (long long)H * dim + (long long)h * dim, vo = 2LL * H * dim + (long long)h * vdim;
+  // bf16 projections carry 8 mantissa bits: their silu may use the hardware exponential and reciprocal
+  auto act = [](float z) { return sizeof(TA) == 2 ? z * __frcp_rn(1.0f + __expf(-z)) : silu(z); };
+  float pq[2][8], pk[2][8], pv[8];
+  auto fetch = [&](int t0) {
+    const int cn = min(C, n - t0), d8 = dim / 8, v8 = VB / 8;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int idx = threadIdx.x + 256 * k, r = idx / d8, c = (idx % d8) * 8;
+      if (idx < C * d8 && r < cn) {
+        const TA* row = qkv + (long long)(row0 + t0 + r) * ld;
+        ld8(row + qo + c, pq[k]);
+        ld8(row + ko + c, pk[k]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) pq[k][x] = pk[k][x] = 0.f;
+      }
+    }
+    const int r = threadIdx.x / v8, c = vb * VB + (threadIdx.x % v8) * 8;
+    if (threadIdx.x < C * v8 && r < cn && c < vdim) ld8(qkv + (long long)(row0 + t0 + r) * ld + vo + c, pv);
+    else {
+#pragma unroll
+      for (int x = 0; x < 8; ++x) pv[x] = 0.f;
+    }
+  };
+  if (VEC) fetch(0);
   for (int t0 = 0; t0 < n; t0 += C) {
     const int cn = min(C, n - t0);
     __syncthreads();
-    for (int i = threadIdx.x; i < C * dim; i += 256) {
-      const int r = i / dim, d = i % dim;
-      float qv = 0.f, kv = 0.f;
-      if (r < cn) {
-        const TA* row = qkv + (long long)(row0 + t0 + r) * ld;
-        qv = silu(ldf(row, qo + d));
-        kv = silu(ldf(row, ko + d));
+    if (VEC) {
+      const int d8 = dim / 8, v8 = VB / 8;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int idx = threadIdx.x + 256 * k, r = idx / d8, c = (idx % d8) * 8;
+        if (idx < C * d8) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            Qs[r * kd + c + x] = act(pq[k][x]);
+            Ks[r * kd + c + x] = act(pk[k][x]);
+          }
+        }
       }
-      Qs[r * kd + d] = qv;
-      Ks[r * kd + d] = kv;
-    }
-    for (int i = threadIdx.x; i < C * VB; i += 256) {
-      const int r = i / VB, c = vb * VB + i % VB;
-      Vs[i] = (r < cn && c < vdim) ? silu(ldf(qkv + (long long)(row0 + t0 + r) * ld, vo + c)) : 0.f;
+      if (threadIdx.x < C * v8) {
+        const int r = threadIdx.x / v8, c = (threadIdx.x % v8) * 8;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) Vs[r * VB + c + x] = act(pv[x]);
+      }
+      if (t0 + C < n) fetch(t0 + C);
+    } else {
+      for (int i = threadIdx.x; i < C * dim4; i += 256) {
+        const int r = i / dim4, d = i % dim4;
+        float qv = 0.f, kv = 0.f;
+        if (r < cn && d < dim) {
+          const TA* row = qkv + (long long)(row0 + t0 + r) * ld;
+          qv = silu(ldf(row, qo + d));
+          kv = silu(ldf(row, ko + d));
+        }
+        Qs[r * kd + d] = qv;
+        Ks[r * kd + d] = kv;
+      }
+      for (int i = threadIdx.x; i < C * VB; i += 256) {
+        const int r = i / VB, c = vb * VB + i % VB;
+        Vs[i] = (r < cn && c < vdim) ? silu(ldf(qkv + (long long)(row0 + t0 + r) * ld, vo + c)) : 0.f;
+      }
     }
     __syncthreads();
-    // A[i][j] = a^(i-j) q_i . k_j  (j <= i)
-    for (int idx = threadIdx.x; idx < C * C; idx += 256) {
-      const int i = idx / C, j = idx % C;
-      float s = 0.f;
-      if (j <= i) {
-        for (int d = 0; d < dim; ++d) s = fmaf(Qs[i * kd + d], Ks[j * kd + d], s);
-        s *= ap[i - j];
+    {  // A[i][j] = a^(i-j) q_i . k_j  (j <= i): a 2 x 2 block per thread, float4 along the key dimension
+      const int i0 = 2 * (threadIdx.x / 16), j0 = 2 * (threadIdx.x % 16);
+      float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
+      if (j0 <= i0 + 1) {
+        const float4* qa = reinterpret_cast<const float4*>(Qs + i0 * kd);
+        const float4* qb = reinterpret_cast<const float4*>(Qs + (i0 + 1) * kd);
+        const float4* ka = reinterpret_cast<const float4*>(Ks + j0 * kd);
+        const float4* kb = reinterpret_cast<const float4*>(Ks + (j0 + 1) * kd);
+        for (int d = 0; d < dim4 / 4; ++d) {
+          const float4 q0 = qa[d], q1 = qb[d], k0 = ka[d], k1 = kb[d];
+          s00 = fmaf(q0.x, k0.x, fmaf(q0.y, k0.y, fmaf(q0.z, k0.z, fmaf(q0.w, k0.w, s00))));
+          s01 = fmaf(q0.x, k1.x, fmaf(q0.y, k1.y, fmaf(q0.z, k1.z, fmaf(q0.w, k1.w, s01))));
+          s10 = fmaf(q1.x, k0.x, fmaf(q1.y, k0.y, fmaf(q1.z, k0.z, fmaf(q1.w, k0.w, s10))));
+          s11 = fmaf(q1.x, k1.x, fmaf(q1.y, k1.y, fmaf(q1.z, k1.z, fmaf(q1.w, k1.w, s11))));
+        }
       }
-      As[idx] = s;
+      As[i0 * C + j0] = j0 <= i0 ? s00 * ap[i0 - j0] : 0.f;
+      As[i0 * C + j0 + 1] = j0 + 1 <= i0 ? s01 * ap[i0 - j0 - 1] : 0.f;
+      As[(i0 + 1) * C + j0] = j0 <= i0 + 1 ? s10 * ap[i0 + 1 - j0] : 0.f;
+      As[(i0 + 1) * C + j0 + 1] = j0 + 1 <= i0 + 1 ? s11 * ap[i0 - j0] : 0.f;
     }
     __syncthreads();
-    // outputs of the thread's rows i = grp * rpt + r
-    float acc[8];
+    // outputs of the thread's rows i = grp * rpt + r: a^(i+1) q_i . S[:, v]  +  sum_j A[i][j] v_j
+    float acc[rpt];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
-    for (int d = 0; d < dim; ++d) {
-      const float sv = Ss[d * VB + vl];
+    for (int r = 0; r < rpt; ++r) acc[r] = 0.f;
+    for (int d = 0; d < dim4; d += 4) {
+      const float s0 = Ss[d * VB + vl], s1 = Ss[(d + 1) * VB + vl], s2 = Ss[(d + 2) * VB + vl], s3 = Ss[(d + 3) * VB + vl];
 #pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (r < rpt) acc[r] = fmaf(Qs[(grp * rpt + r) * kd + d], sv, acc[r]);
+      for (int r = 0; r < rpt; ++r) {
+          const float4 q4 = *reinterpret_cast<const float4*>(Qs + (grp * rpt + r) * kd + d);
+          acc[r] = fmaf(q4.x, s0, fmaf(q4.y, s1, fmaf(q4.z, s2, fmaf(q4.w, s3, acc[r]))));
+        }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
-      if (r < rpt) acc[r] *= ap[grp * rpt + r + 1];
-    for (int j = 0; j < C; ++j) {
-      const float vv = Vs[j * VB + vl];
+    for (int r = 0; r < rpt; ++r) acc[r] *= ap[grp * rpt + r + 1];
+    for (int j = 0; j < C; j += 4) {
+      const float v0 = Vs[j * VB + vl], v1 = Vs[(j + 1) * VB + vl], v2 = Vs[(j + 2) * VB + vl], v3 = Vs[(j + 3) * VB + vl];
 #pragma unroll
-      for (int r = 0; r < 8; ++r)
-        if (r < rpt) acc[r] = fmaf(As[(grp * rpt + r) * C + j], vv, acc[r]);
+      for (int r = 0; r < rpt; ++r) {
+          const float4 a4 = *reinterpret_cast<const float4*>(As + (grp * rpt + r) * C + j);
+          acc[r] = fmaf(a4.x, v0, fmaf(a4.y, v1, fmaf(a4.z, v2, fmaf(a4.w, v3, acc[r]))));
+        }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < rpt; ++r) {
       const int i = grp * rpt + r;
-      if (r < rpt && i < cn && v_ok) out[(long long)(row0 + t0 + i) * ((long long)H * vdim) + (long long)h * vdim + v] = acc[r];
+      if (i < cn && v_ok) out[(long long)(row0 + t0 + i) * ((long long)H * vdim) + (long long)h * vdim + v] = acc[r];
     }
     __syncthreads();  // every read of the old state is done
-    // state: thread = value column x key dimensions d = grp, grp + ngrp, ...
+    // state: thread = value column x key dimensions 4 (grp + ngrp k) .. + 4
     float vw[C];
 #pragma unroll
     for (int j = 0; j < C; ++j) vw[j] = j < cn ? Vs[j * VB + vl] * ap[cn - 1 - j] : 0.f;
     const float ac = ap[cn];
-    for (int d = grp; d < dim; d += ngrp) {
-      float s = ac * Ss[d * VB + vl];
+    for (int d = 4 * grp; d < dim4; d += 4 * ngrp) {
+      float s0 = ac * Ss[d * VB + vl], s1 = ac * Ss[(d + 1) * VB + vl], s2 = ac * Ss[(d + 2) * VB + vl], s3 = ac * Ss[(d + 3) * VB + vl];
 #pragma unroll
-      for (int j = 0; j < C; ++j) s = fmaf(Ks[j * kd + d], vw[j], s);
-      Ss[d * VB + vl] = s;
+      for (int j = 0; j < C; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(Ks + j * kd + d);
+        s0 = fmaf(k4.x, vw[j], s0); s1 = fmaf(k4.y, vw[j], s1); s2 = fmaf(k4.z, vw[j], s2); s3 = fmaf(k4.w, vw[j], s3);
+      }
+      Ss[d * VB + vl] = s0; Ss[(d + 1) * VB + vl] = s1; Ss[(d + 2) * VB + vl] = s2; Ss[(d + 3) * VB + vl] = s3;
     }
   }
   __syncthreads();
@@ -731,28 +796,48 @@ extern "C" int pg_linear_attn_scan(const void* qkv, long long ld, float* state, 
 #undef PG_SCAN
 }
 
+template <typename TA, bool VEC, int VB>
+static int launch_chunked(const void* qkv, long long ld, float* state, const float* decay, float* out, const int* row0, const int* n, const int* ctx,
+                          const int* slot, int entries, int H, int dim, int vdim, size_t smem, cudaStream_t st) {
+  auto kern = linear_attn_chunked_kernel<TA, VEC, VB>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+  kern<<<dim3((vdim + VB - 1) / VB, H, entries), 256, smem, st>>>(static_cast<const TA*>(qkv), ld, state, decay, out, row0, n, ctx, slot, H, dim, vdim);
+  PG_RET();
+}
+
 extern "C" int pg_linear_attn_chunked(const void* qkv, long long ld, float* state, const float* decay, float* out, const int* entry_row0,
                                       const int* entry_n, const int* entry_ctx, const int* entry_slot, int entries, int H, int dim, int vdim,
                                       int act_f32, void* stream) {
   if (entries <= 0 || H <= 0 || dim <= 0 || vdim <= 0 || entries > 65535 || H > 65535) return PG_ERR_ARG;
   int VB = 64;
   while (VB > 8 && VB / 2 >= vdim) VB /= 2;
-  auto bytes = [&](int vb) { return ((size_t)2 * 32 * (dim + 1) + 32 * vb + 32 * 32 + (size_t)dim * vb + 33) * sizeof(float); };
+  // narrower value blocks (the scores are recomputed per block) only while the grid does not even fill the SMs once
+  while (VB > 16 && (long long)((vdim + VB - 1) / VB) * H * entries < (long long)pg::num_sms()) VB /= 2;
+  const int dim4 = (dim + 3) & ~3;
+  auto bytes = [&](int vb) { return ((size_t)2 * 32 * (dim4 + 4) + 32 * vb + 32 * 32 + (size_t)dim4 * vb + 36) * sizeof(float); };
   while (VB > 8 && bytes(VB) > 200 * 1024) VB /= 2;
   const size_t smem = bytes(VB);
   if (smem > 200 * 1024) return PG_ERR_ARG;
-  dim3 grid((vdim + VB - 1) / VB, H, entries);
   cudaStream_t st = PG_ST(stream);
+  // 16-byte fetches: every head's q / k / v slice of a row starts on an 8-element boundary
+  const bool vec = dim % 8 == 0 && vdim % 8 == 0 && dim <= 128 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
+#define PG_CHUNK(TA, VEC, VBV) \
+  return launch_chunked<TA, VEC, VBV>(qkv, ld, state, decay, out, entry_row0, entry_n, entry_ctx, entry_slot, entries, H, dim, vdim, smem, st)
+#define PG_CHUNK_VB(TA, VEC)          \
+  do {                                \
+    if (VB == 64) PG_CHUNK(TA, VEC, 64); \
+    if (VB == 32) PG_CHUNK(TA, VEC, 32); \
+    if (VB == 16) PG_CHUNK(TA, VEC, 16); \
+    PG_CHUNK(TA, VEC, 8);             \
+  } while (0)
   if (act_f32) {
-    auto kern = linear_attn_chunked_kernel<float>;
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
-    kern<<<grid, 256, smem, st>>>(static_cast<const float*>(qkv), ld, state, decay, out, entry_row0, entry_n, entry_ctx, entry_slot, H, dim, vdim, VB);
-  } else {
-    auto kern = linear_attn_chunked_kernel<bf16>;
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
-    kern<<<grid, 256, smem, st>>>(static_cast<const bf16*>(qkv), ld, state, decay, out, entry_row0, entry_n, entry_ctx, entry_slot, H, dim, vdim, VB);
+    if (vec) PG_CHUNK_VB(float, true);
+    PG_CHUNK_VB(float, false);
   }
-  PG_RET();
+  if (vec) PG_CHUNK_VB(bf16, true);
+  PG_CHUNK_VB(bf16, false);
+#undef PG_CHUNK_VB
+#undef PG_CHUNK
 }
 
 template <typename TA, int VC, bool VEC>

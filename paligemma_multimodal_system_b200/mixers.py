@@ -162,7 +162,7 @@ class TokenSideInput:
 
     def __call__(self, h, b, table, prec):
         T = h.shape[0]
-        z = seq_ops.linear(h, self.w_gate, prec.empty(T, self.n_pad))
+        z = seq_ops.linear(h, self.w_gate, torch.empty(T, self.n_pad, device="cuda", dtype=torch.float32))  # fp32: split-K when T is small
         gz = prec.empty(T, self.n_pad)
         seq_ops.side_gate(z, b.tokens, table, self.index * self.n, gz, self.n)
         return seq_ops.linear(gz, self.w_proj, torch.empty(T, self.D, device="cuda", dtype=torch.float32))

@@ -171,7 +171,7 @@ def geglu(gu, out):
 
 def side_gate(z, tokens, table, col0, out, n):
     rows, n_pad = out.shape
-    assert z.dtype == out.dtype == table.dtype
+    assert z.dtype == torch.float32 and out.dtype == table.dtype
     _lib.check(_lib.lib().pg_side_gate(z.data_ptr(), z.stride(0), tokens.data_ptr(), table.data_ptr(), table.stride(0), int(col0), out.data_ptr(),
                                        out.stride(0), rows, int(n), n_pad, int(out.dtype == torch.float32), _lib.stream()), "pg_side_gate")
 
