@@ -47,7 +47,7 @@ __device__ __forceinline__ void split3(float p, float q, uint32_t& hi, uint32_t&
 }
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(128) attn_ragged_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+__global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                                                               const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                               const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                               const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,

@@ -546,7 +546,7 @@ __global__ void __launch_bounds__(256) linear_attn_scan_kernel(const TA* __restr
 // VEC: the block's q / k / v rows are fetched with 16-byte loads ONE BLOCK AHEAD into registers (<= 2 + 2 + 1 loads per thread:
 // dim <= 128), so the memory round trip of block b + 1 hides behind the arithmetic of block b.
 template <typename TA, bool VEC, int VB>
-__global__ void __launch_bounds__(256) linear_attn_chunked_kernel(const TA* __restrict__ qkv, long long ld, float* __restrict__ state,
+__global__ void __launch_bounds__(256, 2) linear_attn_chunked_kernel(const TA* __restrict__ qkv, long long ld, float* __restrict__ state,
                                                                   const float* __restrict__ decay, float* __restrict__ out,
                                                                   const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                                   const int* __restrict__ entry_ctx, const int* __restrict__ entry_slot, int H,
