@@ -391,7 +391,7 @@ def main():
     ap.add_argument("--no-serving", action="store_true", help="skip the continuous-batching sample (N = 1 only)")
     ap.add_argument("--no-configs", action="store_true", help="skip the cfg2 / cfg4 / cfg5 / strong-scaling measurements")
     # --arch mapedra: the Mapedra decoder beside the Gemma decoder at equal layer sizes (paligemma_multimodal_system_b200/bench_seq.py);
-    # the default (paligemma) workload and its JSON contract are untouched by these flags
+    # the default (paligemma) workload and its JSON line are untouched by these flags
     ap.add_argument("--arch", default="paligemma", choices=["paligemma", "mapedra"])
     ap.add_argument("--width", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
