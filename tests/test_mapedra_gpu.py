@@ -376,6 +376,24 @@ def test_long_decoding_across_page_borders(base):
     assert rel_err(run_cut(eng, "a", tk, [40, 1]), ref) < F32_TOL  # 170 single-token steps over the borders at 64, 128, 192
 
 
+def test_long_context_decode_splits_keys_and_grows_the_page_table():
+    """A 1100-token prompt, then 40 single-token steps through the replayed decode graph: the decode attention runs with several
+    key splits, the lightning state carries over 1100 tokens with a decay close to one."""
+    cfg = make_cfg([attn_layer(heads=4, kv_heads=2, dim=64, vdim=64, rot=32, ff=0), light_layer(heads=2, dim=32, vdim=32, decay=(0.999, 0.97), ff=64)],
+                   width=64, vocab=90, side=8)
+    w = O.random_weights(cfg, seed=31)
+    tk = toks(1140, 90, 5)
+    ref = O.forward(cfg, w, tk)
+    for dtype, tol in ((torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)):
+        eng = engine_for(cfg, w, dtype, max_tokens=1152 + 64)
+        poison(eng)
+        head = eng.step([("a", tk[:1000], [999])])
+        body = eng.step([("a", tk[1000:1100], list(range(100)))])
+        tail = torch.cat([eng.step([("a", [t], [0])]) for t in tk[1100:]])
+        assert rel_err(torch.cat([head, body, tail]), torch.cat([ref[999:1000], ref[1000:]])) < tol
+        assert len(eng._decode_graphs) >= 1 and all(g["graph"] is not None for g in eng._decode_graphs.values() if g["seen"] >= 2)
+
+
 def test_first_tokens_of_a_sequence(base):
     w, tk, ref = base
     eng = engine_for(BASE_CFG, w, torch.float32)
@@ -395,6 +413,9 @@ OTHER_SIZES = [
     # lightning only, feed-forward on every layer, decay exactly one
     make_cfg([light_layer(heads=1, dim=64, vdim=64, decay=(1.0,), ff=128), light_layer(heads=4, dim=32, vdim=16, decay=(0.5, 0.5, 0.5, 0.5), ff=64)],
              width=64, vocab=64, groups=2, side=16),
+    # head sizes outside the tensor-core instantiations, rotation over the whole head, three norm groups, wide lightning heads
+    make_cfg([attn_layer(heads=4, kv_heads=2, dim=48, vdim=96, rot=48, ff=72), light_layer(heads=2, dim=128, vdim=128, decay=(0.99, 0.9), ff=0),
+              attn_layer(heads=12, kv_heads=3, dim=16, vdim=8, rot=4, scaling=False, ff=0)], width=96, vocab=500, groups=3, side=24),
     # attention only, big heads, wide values
     make_cfg([attn_layer(heads=2, kv_heads=1, dim=128, vdim=160, rot=64, ff=0), attn_layer(heads=1, kv_heads=1, dim=96, vdim=32, rot=96, ff=256)],
              width=128, vocab=256, groups=8, side=8),
