@@ -63,7 +63,7 @@ int pg_debug_set_attn_trace(long long* device_buffer); /* same for pg_attention_
  */
 int pg_gemm_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo,
                  const float* bias, const float* resid, long long ldr, int tokens, int features, int K, int mode,
-                 int act_gelu, float scale, int swap, int split_k, void* stream);
+                 int act_gelu /* 0 none, 1 gelu(tanh), 2 relu(x)^2: bf16 epilogue */, float scale, int swap, int split_k, void* stream);
 
 /*
  * pg_gemm_bf16 with per-call-site extras; `fusion` may be NULL (= pg_gemm_bf16).  zero_buf and stats belong to the swap-AB
@@ -283,6 +283,12 @@ int pg_gemm_simt(const void* x, long long ldx, const void* w, long long ldw, voi
                  int K, int in_f32, int out_f32, void* stream);
 
 /* out[t, 0:D] (fp32) = table[tokens[t], col0 : col0 + D] * scale  (embedding lookup; table bf16 or fp32, pitch ld). */
+/* grid.z = batch independent products out_b = x_b w_b^T; operand b starts batch_* elements after operand b - 1 (per-head
+ * projections: x a column slice per head, w one matrix per head). */
+int pg_gemm_simt_batched(const void* x, long long ldx, long long batch_x, const void* w, long long ldw, long long batch_w, void* out,
+                         long long ldo, long long batch_out, int tokens, int features, int K, int batch, int in_f32, int out_f32,
+                         void* stream);
+
 int pg_embed_rows(const int* tokens, const void* table, long long ld, int col0, float* out, int rows, int D, float scale,
                   int table_f32, void* stream);
 
@@ -299,6 +305,9 @@ int pg_rmsnorm_gate(const float* o, const float* w, const void* gate, long long 
 
 /* out[t, f] = gelu_tanh(gu[t, f]) * gu[t, F + f]: the gate || up product when it is not fused into the GEMM epilogue. */
 int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int act_f32, void* stream);
+
+/* x[t, f] <- relu(x[t, f])^2 in place (rows x F, pitch ld): the activation when it is not fused into the GEMM epilogue. */
+int pg_relu2(void* x, long long ld, int rows, int F, int act_f32, void* stream);
 
 /* out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], col0 + j] for j < n, 0 for n <= j < n_pad (per-token side input: a
  * gate projection of the residual, fp32, times the token's own low-dimensional embedding slice). */
@@ -321,21 +330,26 @@ int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* ro
  * entry_n == 1 to pg_attn_decode.
  * pg_attn_decode handles ONLY entries with entry_n == 1 (decoded tokens): nsplit CTAs per (entry, k/v head) share the keys,
  * every warp streams its own 32-key tiles from the pages; with nsplit > 1 the partial (max, sum, accumulator) triples go
- * through `partial` (fp32 [entries, H, nsplit, vdim + 2]) and a merge launch. */
+ * through `partial` (fp32 [entries, H, nsplit, vdim + 2]) and a merge launch.
+ * krow / vrow: elements between consecutive cache rows of k_pages / v_pages (<= 0: G * dim, G * vdim).  A cache that keeps one
+ * row per token serving as key AND value (latent attention: G = 1, v_pages == k_pages, vrow == krow, the value is the first
+ * vdim columns of the key row) is staged once per tile.  gate_per_head != 0: one gate scalar per head, gate[t * ldg + h]. */
 int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                    int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
-                   void* stream);
+                   long long krow, long long vrow, int gate_per_head, void* stream);
 /* pg_attn_ragged for bf16 activations on the tensor cores (mma.sync m16n8k16): S = Q K^T from the bf16 operands with fp32
  * accumulation; the fp32 probabilities are cut into three bf16 terms each and P V runs as three passes over the bf16 values,
- * so no probability is rounded to bf16.  Head sizes (dim, vdim) in {(32,32), (64,64), (128,128), (64,128), (128,64)}; anything
- * else returns PG_ERR_ARG and belongs to pg_attn_ragged. */
+ * so no probability is rounded to bf16.  Head sizes (dim, vdim) in {(32,32), (64,64), (128,128), (64,128), (128,64), (96,64),
+ * (192,128)}; anything else returns PG_ERR_ARG and belongs to pg_attn_ragged. */
 int pg_attn_ragged_mma(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                        const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                       int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, void* stream);
+                       int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single,
+                       int gate_per_head, void* stream);
 int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                   int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream);
+                   int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,
+                   long long vrow, int gate_per_head, void* stream);
 
 /* Decayed linear attention on qkv[t] = [q heads | k heads | v heads | ...] (q, k: H x dim, v: H x vdim; silu applied here):
  * per head S <- decay[h] * S + k v^T, out[t, h * vdim + :] = S^T q (fp32).  state: fp32 [slots, H, dim, vdim]; entry e
@@ -348,6 +362,60 @@ int pg_linear_attn_scan(const void* qkv, long long ld, float* state, const float
 int pg_linear_attn_chunked(const void* qkv, long long ld, float* state, const float* decay, float* out, const int* entry_row0,
                            const int* entry_n, const int* entry_ctx, const int* entry_slot, int entries, int H, int dim, int vdim,
                            int act_f32, void* stream);
+
+/* ---- multi-stream residual ("hyper-connections"): xs fp32 [rows, S, D], S <= 8 -------------------------------------------------
+ * pg_embed_streams: xs[t, s, :] = table[tokens[t], 0:D] * scale for every stream s.
+ * pg_stream_mix_norm, per row, in this order:
+ *   y != NULL:         x_to <- sum_s mix[s * S + to] x_s + write_coef[to] * y[t, :]   (all streams from the old ones, in place)
+ *   read_coef != NULL: u = sum_s read_coef[s] x_s;  out_act[t, :] = u / sqrt(mean(u^2) + eps) * norm_w  (norm_w NULL: no weight)
+ * y, mix, write_coef come together; read_coef and out_act come together. */
+int pg_embed_streams(const int* tokens, const void* table, long long ld, float* xs, int rows, int S, int D, float scale, int table_f32,
+                     void* stream);
+int pg_stream_mix_norm(float* xs, const float* y, long long ldy, const float* mix, const float* write_coef, const float* read_coef,
+                       const float* norm_w, void* out_act, int rows, int S, int D, float eps, int out_f32, void* stream);
+
+/* ---- latent attention: the cache keeps one row [c (rank) | r (rot)] per token ---------------------------------------------------
+ * pg_latent_prepare: proj[t] = [q latent (q_rank) | kv latent (rank) | key part (rot) | ...] (pitch ld).  cq_out[t, :] =
+ *   rms(q latent) * q_norm (skipped when q_rank == 0); cache row of position pos[t] <- [rms(kv latent) * c_norm | key part with
+ *   its first rot_dims dimensions rotated in interleaved pairs by pos[t] * freq[i]].  pages: [.., page, rank + rot].
+ * pg_rotate_heads: for every row and head, n elements at src[t * ld_src + h * head_stride_src ..] are copied to
+ *   dst[t * ld_dst + h * head_stride_dst ..] with the first rot_dims rotated the same way.
+ * pg_latent_gather: lat[dense_row0[e] + j, 0:rank] <- cached row j of entry e, j < ctx + n (width = elements per cache row).
+ * pg_latent_pack_kv: up[row] = [H x dim plain key parts | H x vdim values] (pitch ld_up) of the gathered rows ->
+ *   k_out[row, h, :] = [plain (dim) | cached rotated part (rot)], v_out[row, h, :]. */
+int pg_latent_prepare(const void* proj, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
+                      int page, const double* freq, const float* q_norm, const float* c_norm, void* cq_out, void* pages, int rows,
+                      int q_rank, int rank, int rot, int rot_dims, float eps, int act_f32, void* stream);
+int pg_rotate_heads(const void* src, long long ld_src, long long head_stride_src, void* dst, long long ld_dst, long long head_stride_dst,
+                    const int* pos, const double* freq, int rows, int H, int n, int rot_dims, int act_f32, void* stream);
+int pg_latent_gather(const void* pages, const int* page_table, int max_pages, int page, const int* dense_row0, const int* entry_n,
+                     const int* entry_ctx, void* lat, int entries, int max_len, int rank, int width, int act_f32, void* stream);
+int pg_latent_pack_kv(const void* up, long long ld_up, const void* pages, const int* page_table, int max_pages, int page,
+                      const int* dense_row0, const int* entry_n, const int* entry_ctx, void* k_out, void* v_out, int entries, int max_len,
+                      int H, int dim, int rot, int vdim, int rank, int act_f32, void* stream);
+
+/* ---- routed feed-forward (mixture of experts), everything on the device ---------------------------------------------------------
+ * pg_moe_route: logits fp32 [tokens, n_all] (pitch ld).  p = softmax(logits); choice = p + correction (NULL: none); with
+ *   group_count > 1 the outputs form group_count equal runs of neighbours and only the group_keep runs with the largest best
+ *   choice stay eligible; ids[t, 0:top] = the largest choices (descending), weights[t, k] = p[ids] / (sum + 1e-20) * scale.
+ *   Outputs >= n_real are identity experts.  counts[e] (e < n_real) = pairs routed to expert e (zeroed here).
+ * pg_moe_plan: offsets[0..n_real] (exclusive scan of counts), plan[0] = tiles, plan[4 + 3i ..] = (expert, first sorted row, rows)
+ *   of tile i (pg_moe_tile_rows() rows at most; max_tiles >= ceil(pairs / tile) + n_real), sorted_pair[row] = pair t * top + k,
+ *   pair_row[pair] = its sorted row (-1: identity expert).  fill: int32 [n_real] scratch.
+ * pg_moe_gemm: out[row, f] = act(sum_k x[src(row), k] * w[expert(row)][f, k]) for the rows of every tile; src(row) =
+ *   sorted_pair[row] / src_div when src_div > 0, else row.  w: [n_real] matrices [F, K] (pitch ldw, expert_stride elements apart).
+ *   act: 0 none, 2 relu(x)^2.
+ * pg_moe_combine: y[t, :] = sum_k weights[t, k] * (pair_row[t, k] < 0 ? h[t, :] : expert_out[pair_row[t, k], :]) + shared_out[t, :]
+ *   (shared_out may be NULL). */
+int pg_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int* counts, int tokens, int n_all,
+                 int n_real, int top, int group_count, int group_keep, float scale, void* stream);
+int pg_moe_tile_rows(void);
+int pg_moe_plan(const int* counts, const int* ids, int* offsets, int* fill, int* plan, int* sorted_pair, int* pair_row, int pairs,
+                int n_real, int max_tiles, void* stream);
+int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
+                void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, void* stream);
+int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
+                   long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream);
 
 #ifdef __cplusplus
 }

@@ -70,11 +70,24 @@ SIGNATURES = {
     "pg_geglu": [p, i64, p, i64, i32, i32, i32, p],
     "pg_side_gate": [p, i64, p, p, i64, i32, p, i64, i32, i32, i32, i32, p],
     "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, p],
-    "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p],
-    "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, p],
-    "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, p],
+    "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, i64, i64, i32, p],
+    "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p],
+    "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i64, i64, i32, p],
     "pg_linear_attn_scan": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_linear_attn_chunked": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
+    "pg_gemm_simt_batched": [p, i64, i64, p, i64, i64, p, i64, i64, i32, i32, i32, i32, i32, i32, p],
+    "pg_embed_streams": [p, p, i64, p, i32, i32, i32, f32, i32, p],
+    "pg_stream_mix_norm": [p, p, i64, p, p, p, p, p, i32, i32, i32, f32, i32, p],
+    "pg_latent_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
+    "pg_rotate_heads": [p, i64, i64, p, i64, i64, p, p, i32, i32, i32, i32, i32, p],
+    "pg_latent_gather": [p, p, i32, i32, p, p, p, p, i32, i32, i32, i32, i32, p],
+    "pg_latent_pack_kv": [p, i64, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, p],
+    "pg_relu2": [p, i64, i32, i32, i32, p],
+    "pg_moe_route": [p, i64, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, p],
+    "pg_moe_tile_rows": [],
+    "pg_moe_plan": [p, p, p, p, p, p, p, i32, i32, i32, p],
+    "pg_moe_gemm": [p, i64, p, i32, p, i64, i64, p, i64, p, i32, i32, i32, i32, i32, i32, p],
+    "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
 }
 _RESTYPE = {"pg_launch_count": i64}
 
@@ -139,7 +152,7 @@ def require_device():
 # ------------------------------------------------------------------------------------------------------------------
 # thin typed wrappers (argument checking that needs tensor metadata lives here; kernels check the rest)
 # ------------------------------------------------------------------------------------------------------------------
-def gemm(x, w, out, *, mode, bias=None, resid=None, act_gelu=False, scale=1.0, swap=-1, split_k=1, features=None, resid_row_mod=0,
+def gemm(x, w, out, *, mode, bias=None, resid=None, act_gelu=0, scale=1.0, swap=-1, split_k=1, features=None, resid_row_mod=0,
          out_row_map=None):
     """out[t,f] (mode-dependent) from x [T,K] bf16 and w [F,K] bf16 (nn.Linear layout).  resid_row_mod = N > 0: `resid` is an
     [N, F] table and token t takes row t % N (position embeddings).  out_row_map int32 [T]: token t goes to row out_row_map[t]

@@ -4,6 +4,8 @@ The `KVCache` of modeling_gemma.py gives every batch row a fixed run of pages; h
 A model describes what each of its layers keeps per sequence (`cache_layout()`):
 
     ("kv", key_width, value_width)      one key row and one value row per token  -> pages [num_pages, 64, width]
+    ("latent", width)                   ONE row per token from which keys and values of every head are derived (latent
+                                        attention: compressed kv vector + shared rotated key part) -> k_pages only
     ("state", shape)                    one fp32 tensor per sequence             -> [num_slots, *shape]
     None                                nothing
 
@@ -68,9 +70,11 @@ class SequenceStore:
             if allocate and spec is not None and spec[0] == "kv":
                 k = torch.zeros(num_pages, PAGE, spec[1], device=device, dtype=dtype)
                 v = torch.zeros(num_pages, PAGE, spec[2], device=device, dtype=dtype)
+            elif allocate and spec is not None and spec[0] == "latent":
+                k = torch.zeros(num_pages, PAGE, spec[1], device=device, dtype=dtype)
             elif allocate and spec is not None and spec[0] == "state":
                 s = torch.zeros(self.num_slots, *spec[1], device=device, dtype=torch.float32)
-            elif spec is not None and spec[0] not in ("kv", "state"):
+            elif spec is not None and spec[0] not in ("kv", "latent", "state"):
                 raise ValueError(f"unknown cache kind {spec[0]!r}")
             self.k_pages.append(k)
             self.v_pages.append(v)

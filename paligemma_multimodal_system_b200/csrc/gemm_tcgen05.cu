@@ -128,6 +128,12 @@ PG_DEVINL TileInfo decode_tile(int tile, int m_blocks, int n_blocks, int total_k
   return t;
 }
 
+// activation of the bf16 epilogue (GemmArgs::act_gelu): 1 = gelu(tanh), 2 = relu(x)^2
+PG_DEVINL float epilogue_act(float x, int act) {
+  if (act == 2) { const float r = fmaxf(x, 0.f); return r * r; }
+  return gelu_tanh_fast(x);
+}
+
 PG_DEVINL void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
 
 
@@ -147,7 +153,7 @@ PG_DEVINL void swap_tile_epilogue(const GemmArgs& args, uint32_t taddr, int fr, 
   const char* res = (MODE == PG_EPI_F32 && args.resid != nullptr)
                         ? reinterpret_cast<const char*>(args.resid + static_cast<long long>(j_base + col_begin) * args.ldr + fr) : nullptr;
   const long long rstep = args.ldr * 4;
-  const bool gelu = MODE == PG_EPI_BF16 && args.act_gelu != 0;
+  const int act = MODE == PG_EPI_BF16 ? args.act_gelu : 0;  // 1: gelu(tanh), 2: relu squared
 #pragma unroll 1
   for (int c0 = col_begin; c0 < BN; c0 += 16) {
     if (c0 >= nvalid) break;  // warp-uniform
@@ -161,7 +167,7 @@ PG_DEVINL void swap_tile_epilogue(const GemmArgs& args, uint32_t taddr, int fr, 
       if (i < n) {
         float x = fmaf(__uint_as_float(r[i]), scale, bias_s);
         if (MODE == PG_EPI_BF16) {
-          if (gelu) x = gelu_tanh_fast(x);
+          if (act) x = epilogue_act(x, act);
           *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16(x);
         } else if (MODE == PG_EPI_F32) {
           if (res != nullptr) x += *reinterpret_cast<const float*>(res);
@@ -391,7 +397,7 @@ PG_DEVINL void rowmajor_tile_epilogue(const GemmArgs& args, uint32_t taddr, int 
   const bool row_ok = tok < args.tokens;
   const float scale = args.scale;
   const bool has_bias = args.bias != nullptr && first_split;
-  const bool gelu = MODE == PG_EPI_BF16 && args.act_gelu != 0;
+  const int act = MODE == PG_EPI_BF16 ? args.act_gelu : 0;  // 1: gelu(tanh), 2: relu squared
   __nv_bfloat16* out_bf = reinterpret_cast<__nv_bfloat16*>(args.out) + static_cast<long long>(tok) * args.ldo;
   const int orow = (MODE == PG_EPI_F32 && args.out_row_map != nullptr && tok < args.tokens) ? __ldg(args.out_row_map + tok) : tok;
   float* out_f = reinterpret_cast<float*>(args.out) + static_cast<long long>(orow) * args.ldo;
@@ -440,9 +446,9 @@ PG_DEVINL void rowmajor_tile_epilogue(const GemmArgs& args, uint32_t taddr, int 
           }
         }
         if (MODE == PG_EPI_BF16) {
-          if (gelu) {
+          if (act) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = gelu_tanh_fast(v[i]);
+            for (int i = 0; i < 16; ++i) v[i] = epilogue_act(v[i], act);
           }
           if (collective) {
 #pragma unroll
@@ -481,7 +487,7 @@ PG_DEVINL void rowmajor_tile_epilogue(const GemmArgs& args, uint32_t taddr, int 
             float x = __uint_as_float(r[ch][i]) * scale;
             if (has_bias) x = fmaf(__ldg(args.bias + f), scale, x);
             if (MODE == PG_EPI_BF16) {
-              if (gelu) x = gelu_tanh_fast(x);
+              if (act) x = epilogue_act(x, act);
               out_bf[f] = __float2bfloat16(x);
             } else if (MODE == PG_EPI_F32) {
               out_f[f] = x + (res != nullptr ? res[f] : 0.f);

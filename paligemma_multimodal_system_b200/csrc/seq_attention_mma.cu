@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
                                                               const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                               const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                               const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
-                                                              int page, int H, int G, float scale, float softcap, int skip_single) {
+                                                              int page, int H, int G, float scale, float softcap, int skip_single, int gate_per_head) {
   constexpr int KS = DIM / 16, NV = VDIM / 8, QP = DIM + 8, VP = 64 + 8;
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
   const int n = entry_n[e], ctx = entry_ctx[e], row0 = entry_row0[e];
@@ -190,7 +190,9 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
       const int col = nv * 8 + 2 * tq;
       float v0 = oacc[nv][2 * half] * inv, v1 = oacc[nv][2 * half + 1] * inv;
       if (gate != nullptr) {
-        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t * ldg + (long long)head * VDIM + col));
+        float2 gg;
+        if (gate_per_head) gg.x = gg.y = __bfloat162float(gate[t * ldg + head]);  // one scalar gate per head
+        else gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t * ldg + (long long)head * VDIM + col));
         v0 *= 1.0f / (1.0f + expf(-gg.x));
         v1 *= 1.0f / (1.0f + expf(-gg.y));
       }
@@ -201,13 +203,13 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 
 template <int DIM, int VDIM>
 int launch(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0, const int* n, const int* ctx,
-           const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, cudaStream_t st) {
+           const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, int gate_per_head, cudaStream_t st) {
   const size_t smem = ((size_t)2 * 64 * (DIM + 8) + (size_t)VDIM * 72) * sizeof(bf16);
   auto kern = attn_ragged_mma_kernel<DIM, VDIM>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   dim3 grid((max_n * (H / G) + 63) / 64, G, entries);
   kern<<<grid, 128, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(kp), static_cast<const bf16*>(vp), static_cast<const bf16*>(gate), ldg,
-                                static_cast<bf16*>(out), row0, n, ctx, pt, max_pages, page, H, G, scale, softcap, skip_single);
+                                static_cast<bf16*>(out), row0, n, ctx, pt, max_pages, page, H, G, scale, softcap, skip_single, gate_per_head);
   pg_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
@@ -216,18 +218,21 @@ int launch(const void* q, const void* kp, const void* vp, const void* gate, long
 
 extern "C" int pg_attn_ragged_mma(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                                   const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                                  int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, void* stream) {
+                                  int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int gate_per_head,
+                                  void* stream) {
   if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || entries > 65535 || G > 65535) return PG_ERR_ARG;
   // 16-byte row loads and bf16x2 gate / output accesses
   if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages) | reinterpret_cast<uintptr_t>(out)) & 15) ||
-      (gate != nullptr && ((reinterpret_cast<uintptr_t>(gate) & 3) || (ldg & 1))))
+      (gate != nullptr && !gate_per_head && ((reinterpret_cast<uintptr_t>(gate) & 3) || (ldg & 1))))
     return PG_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define PG_MMA(D, V) \
   if (dim == D && vdim == V) \
     return launch<D, V>(q, k_pages, v_pages, gate, ldg, out, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, max_n, H, G, scale, \
-                        softcap, skip_single, st)
+                        softcap, skip_single, gate_per_head, st)
   PG_MMA(32, 32);
+  PG_MMA(96, 64);    // explicit-head form of latent attention: [plain | rotated] keys
+  PG_MMA(192, 128);
   PG_MMA(64, 64);
   PG_MMA(128, 128);
   PG_MMA(64, 128);

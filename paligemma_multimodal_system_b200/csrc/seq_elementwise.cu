@@ -55,9 +55,13 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x, long long ldx, const TI* __restrict__ w, long long ldw,
-                                                        TO* __restrict__ out, long long ldo, int T, int F, int K) {
+                                                        TO* __restrict__ out, long long ldo, int T, int F, int K, long long bsx = 0,
+                                                        long long bsw = 0, long long bso = 0) {
   __shared__ float xs[16][64 + 4];
   __shared__ float ws[16][64 + 4];
+  x += blockIdx.z * bsx;  // batched form: grid.z independent products with their own operand offsets
+  w += blockIdx.z * bsw;
+  out += blockIdx.z * bso;
   const int t0 = blockIdx.y * 64, f0 = blockIdx.x * 64;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};
@@ -220,6 +224,17 @@ __global__ void geglu_kernel(const TA* __restrict__ gu, long long ldgu, TA* __re
   st_f(out, t * ldo + f, pg::gelu_tanh(ld_f(gu, t * ldgu + f)) * ld_f(gu, t * ldgu + F + f));
 }
 
+// x[t, f] <- relu(x[t, f])^2 in place (the unfused activation of the exact-precision path)
+template <typename TA>
+__global__ void relu2_kernel(TA* __restrict__ x, long long ld, int F, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / F;
+  const int f = (int)(i % F);
+  const float v = fmaxf(ld_f(x, t * ld + f), 0.f);
+  st_f(x, t * ld + f, v * v);
+}
+
 // out[t, j] = gelu_tanh(z[t, j]) * table[token[t], col0 + j]  for j < n, zero for n <= j < n_pad   (z fp32)
 template <typename TA>
 __global__ void side_gate_kernel(const float* __restrict__ z, long long ldz, const int* __restrict__ tokens, const TA* __restrict__ table, long long ldt,
@@ -247,6 +262,24 @@ extern "C" int pg_gemm_simt(const void* x, long long ldx, const void* w, long lo
     gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K);
   else if (!in_f32 && !out_f32)
     gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K);
+  else
+    return PG_ERR_ARG;
+  PG_RET();
+}
+
+extern "C" int pg_gemm_simt_batched(const void* x, long long ldx, long long batch_x, const void* w, long long ldw, long long batch_w, void* out,
+                                    long long ldo, long long batch_out, int tokens, int features, int K, int batch, int in_f32, int out_f32,
+                                    void* stream) {
+  if (tokens <= 0 || features <= 0 || K <= 0 || batch <= 0 || batch > 65535 || x == nullptr || w == nullptr || out == nullptr) return PG_ERR_ARG;
+  dim3 grid((features + 63) / 64, (tokens + 63) / 64, batch);
+  if (grid.y > 65535) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (in_f32 && out_f32)
+    gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, batch_x, batch_w, batch_out);
+  else if (!in_f32 && out_f32)
+    gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, batch_x, batch_w, batch_out);
+  else if (!in_f32 && !out_f32)
+    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K, batch_x, batch_w, batch_out);
   else
     return PG_ERR_ARG;
   PG_RET();
@@ -304,6 +337,15 @@ extern "C" int pg_geglu(const void* gu, long long ldgu, void* out, long long ldo
     geglu_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(gu), ldgu, static_cast<float*>(out), ldo, F, total);
   else
     geglu_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(gu), ldgu, static_cast<bf16*>(out), ldo, F, total);
+  PG_RET();
+}
+
+extern "C" int pg_relu2(void* x, long long ld, int rows, int F, int act_f32, void* stream) {
+  if (rows <= 0 || F <= 0) return PG_ERR_ARG;
+  const long long total = (long long)rows * F;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act_f32) relu2_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<float*>(x), ld, F, total);
+  else relu2_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<bf16*>(x), ld, F, total);
   PG_RET();
 }
 

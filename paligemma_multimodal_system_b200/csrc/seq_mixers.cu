@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
                                                           const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
                                                           const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                           const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
-                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single) {
+                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single,
+                                                          long long krow, long long vrow, int gate_per_head, int alias) {
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
   const int n = entry_n[e], ctx = entry_ctx[e], row0 = entry_row0[e];
   if (skip_single && n == 1) return;
@@ -130,8 +131,9 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
   extern __shared__ __align__(16) float sm[];
   float* Qs = sm;                    // [32][dimp]
   float* Ks = Qs + 32 * dimp;        // [32][ks]
-  float* Vs = Ks + 32 * ks;          // [32][vdim]
-  float* Ps = Vs + 32 * vdim;        // [8][4][32]
+  float* Vs = alias ? Ks : Ks + 32 * ks;             // [32][vdim]; alias: the values are the first vdim columns of the key rows
+  float* Ps = Ks + 32 * ks + (alias ? 0 : 32 * vdim);  // [8][4][32]
+  const int vst = alias ? ks : vdim;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // query rows: r -> token r / gsz, head g * gsz + r % gsz
   for (int i = threadIdx.x; i < 32 * dimp; i += 256) {
@@ -160,15 +162,16 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
     for (int i = threadIdx.x; i < 32 * dimp; i += 256) {
       const int r = i / dimp, d = i % dimp, j = k0 + r;
       float v = 0.f;
-      if (j <= kmax && d < dim) v = ldf(k_pages, ((long long)pt[j / page] * page + j % page) * ((long long)G * dim) + (long long)g * dim + d);
+      if (j <= kmax && d < dim) v = ldf(k_pages, ((long long)pt[j / page] * page + j % page) * krow + (long long)g * dim + d);
       Ks[r * ks + d] = v;
     }
-    for (int i = threadIdx.x; i < 32 * vdim; i += 256) {
-      const int r = i / vdim, d = i % vdim, j = k0 + r;
-      float v = 0.f;
-      if (j <= kmax) v = ldf(v_pages, ((long long)pt[j / page] * page + j % page) * ((long long)G * vdim) + (long long)g * vdim + d);
-      Vs[i] = v;
-    }
+    if (!alias)
+      for (int i = threadIdx.x; i < 32 * vdim; i += 256) {
+        const int r = i / vdim, d = i % vdim, j = k0 + r;
+        float v = 0.f;
+        if (j <= kmax) v = ldf(v_pages, ((long long)pt[j / page] * page + j % page) * vrow + (long long)g * vdim + d);
+        Vs[i] = v;
+      }
     __syncthreads();
     if (k0 > wlim) continue;  // every row of this warp is past its causal limit
     float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
 #pragma unroll
           for (int c = 0; c < VC; ++c) {
             const int col = lane + 32 * c;
-            if (col < vdim) o[i][c] = fmaf(pv[jj], Vs[(j + jj) * vdim + col], o[i][c]);
+            if (col < vdim) o[i][c] = fmaf(pv[jj], Vs[(j + jj) * vst + col], o[i][c]);
           }
       }
     }
@@ -230,7 +233,7 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
       const int col = lane + 32 * c;
       if (col < vdim) {
         float v = o[i][c] * inv;
-        if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (long long)head * vdim + col));
+        if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (gate_per_head ? (long long)head : (long long)head * vdim + col)));
         stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
       }
     }
@@ -270,7 +273,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
                                                           const TA* __restrict__ gate, long long ldg, TA* __restrict__ out, float* __restrict__ partial,
                                                           const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                           const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
-                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap) {
+                                                          int page, int H, int G, int dim, int vdim, float scale, float softcap, long long krow,
+                                                          long long vrow, int gate_per_head) {
   constexpr int NO = VEC ? 8 * VC : 2 * VC;  // accumulator columns per lane
   const int e = blockIdx.z, g = blockIdx.y, split = blockIdx.x, nsplit = gridDim.x, gsz = H / G;
   if (entry_n[e] != 1) return;
@@ -292,7 +296,6 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
   __syncthreads();
   const int* pt = page_table + (long long)e * max_pages;
   const int ntiles = ctx / 32 + 1;  // keys 0 .. ctx
-  const long long krow = (long long)G * dim, vrow = (long long)G * vdim;
   for (int rb = 0; rb < gsz; rb += 4) {
     const int nr = min(4, gsz - rb);
     float m[4], l[4], o[4][NO];
@@ -438,7 +441,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
       const int head = g * gsz + rb + i;
       if (nsplit == 1) {
         float v = acc / ls;
-        if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (long long)head * vdim + col));
+        if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (gate_per_head ? (long long)head : (long long)head * vdim + col)));
         stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
       } else {
         float* pp = partial + (((long long)e * H + head) * nsplit + split) * (vdim + 2);
@@ -451,7 +454,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
 
 template <typename TA>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
-                                         const int* __restrict__ entry_row0, const int* __restrict__ entry_n, int H, int vdim, int nsplit) {
+                                         const int* __restrict__ entry_row0, const int* __restrict__ entry_n, int H, int vdim, int nsplit,
+                                         int gate_per_head) {
   const int e = blockIdx.y, head = blockIdx.x;
   if (entry_n[e] != 1) return;
   const long long t = entry_row0[e];
@@ -469,7 +473,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, cons
       }
     }
     float v = acc / ls;
-    if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (long long)head * vdim + col));
+    if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (gate_per_head ? (long long)head : (long long)head * vdim + col)));
     stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
   }
 }
@@ -733,35 +737,44 @@ extern "C" int pg_attn_prepare(const void* qkv, long long ld, const int* pos, co
 template <typename TA, int VC>
 static int launch_attn_ragged(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0,
                               const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int max_n, int H, int G,
-                              int dim, int vdim, float scale, float softcap, int skip_single, cudaStream_t st) {
+                              int dim, int vdim, float scale, float softcap, int skip_single, long long krow, long long vrow, int gate_per_head,
+                              cudaStream_t st) {
   const int dimp = (dim + 3) & ~3;
-  const size_t smem = ((size_t)32 * dimp + 32 * (dimp + 4) + 32 * vdim + 8 * 128) * sizeof(float);
+  // one latent row serves as key and value (one k/v head, values = leading key columns): the tile is staged once
+  const int alias = (kp == vp && G == 1 && krow == vrow && vdim <= dim) ? 1 : 0;
+  const size_t smem = ((size_t)32 * dimp + 32 * (dimp + 4) + (alias ? 0 : 32 * vdim) + 8 * 128) * sizeof(float);
   if (smem > 220 * 1024) return PG_ERR_ARG;
   auto kern = attn_ragged_kernel<TA, VC>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   dim3 grid((max_n * (H / G) + 31) / 32, G, entries);
   kern<<<grid, 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp), static_cast<const TA*>(gate), ldg,
-                                static_cast<TA*>(out), row0, n, ctx, pt, max_pages, page, H, G, dim, vdim, scale, softcap, skip_single);
+                                static_cast<TA*>(out), row0, n, ctx, pt, max_pages, page, H, G, dim, vdim, scale, softcap, skip_single, krow, vrow,
+                                gate_per_head, alias);
   PG_RET();
 }
 
 extern "C" int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                              int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32, void* stream) {
-  if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 256 || entries > 65535 || G > 65535)
+                              int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
+                              long long krow, long long vrow, int gate_per_head, void* stream) {
+  if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 512 || entries > 65535 || G > 65535)
     return PG_ERR_ARG;
+  if (krow <= 0) krow = (long long)G * dim;
+  if (vrow <= 0) vrow = (long long)G * vdim;
   cudaStream_t st = PG_ST(stream);
 #define PG_ATTN(TA, VC) \
   return launch_attn_ragged<TA, VC>(q, k_pages, v_pages, gate, ldg, out, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, max_n, \
-                                    H, G, dim, vdim, scale, softcap, skip_single, st)
+                                    H, G, dim, vdim, scale, softcap, skip_single, krow, vrow, gate_per_head, st)
   if (act_f32) {
     if (vdim <= 64) PG_ATTN(float, 2);
     if (vdim <= 128) PG_ATTN(float, 4);
-    PG_ATTN(float, 8);
+    if (vdim <= 256) PG_ATTN(float, 8);
+    PG_ATTN(float, 16);
   }
   if (vdim <= 64) PG_ATTN(bf16, 2);
   if (vdim <= 128) PG_ATTN(bf16, 4);
-  PG_ATTN(bf16, 8);
+  if (vdim <= 256) PG_ATTN(bf16, 8);
+  PG_ATTN(bf16, 16);
 #undef PG_ATTN
 }
 
@@ -843,7 +856,8 @@ extern "C" int pg_linear_attn_chunked(const void* qkv, long long ld, float* stat
 template <typename TA, int VC, bool VEC>
 static int launch_attn_decode(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, float* partial,
                               const int* row0, const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H,
-                              int G, int dim, int vdim, float scale, float softcap, cudaStream_t st) {
+                              int G, int dim, int vdim, float scale, float softcap, long long krow, long long vrow, int gate_per_head,
+                              cudaStream_t st) {
   const int gsz = H / G, dimp = (dim + 7) & ~7;
   const size_t smem = ((size_t)gsz * dimp + 8 * 128 + 64 + (size_t)32 * vdim) * sizeof(float);
   if (smem > 200 * 1024) return PG_ERR_ARG;
@@ -851,10 +865,11 @@ static int launch_attn_decode(const void* q, const void* kp, const void* vp, con
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   kern<<<dim3(nsplit, G, entries), 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp),
                                                      static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), partial, row0, n, ctx, pt, max_pages, page,
-                                                     H, G, dim, vdim, scale, softcap);
+                                                     H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head);
   pg_count_launch(1);
   if (nsplit > 1) {
-    attn_decode_merge_kernel<TA><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit);
+    attn_decode_merge_kernel<TA><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit,
+                                                                  gate_per_head);
     pg_count_launch(1);
   }
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
@@ -862,28 +877,33 @@ static int launch_attn_decode(const void* q, const void* kp, const void* vp, con
 
 extern "C" int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
-                              int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, void* stream) {
-  if (entries <= 0 || nsplit <= 0 || nsplit > 64 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 256 || entries > 65535 ||
+                              int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,
+                              long long vrow, int gate_per_head, void* stream) {
+  if (entries <= 0 || nsplit <= 0 || nsplit > 64 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 512 || entries > 65535 ||
       G > 65535 || (nsplit > 1 && partial == nullptr))
     return PG_ERR_ARG;
+  if (krow <= 0) krow = (long long)G * dim;
+  if (vrow <= 0) vrow = (long long)G * vdim;
   cudaStream_t st = PG_ST(stream);
   // 16-byte loads need every head's key / value row to start on an 8-element boundary and tiles that stay inside a page
-  const bool vec = (dim % 8 == 0) && (vdim % 8 == 0) && (page % 32 == 0) && vdim <= 128 && ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) &&
-                   ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0);
+  const bool vec = (dim % 8 == 0) && (vdim % 8 == 0) && (krow % 8 == 0) && (vrow % 8 == 0) && (page % 32 == 0) && vdim <= 128 &&
+                   ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0);
 #define PG_ATTD(TA, VC, VEC) \
   return launch_attn_decode<TA, VC, VEC>(q, k_pages, v_pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, \
-                                         entries, nsplit, H, G, dim, vdim, scale, softcap, st)
+                                         entries, nsplit, H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head, st)
   if (act_f32) {
     if (vec && vdim <= 64) PG_ATTD(float, 1, true);
     if (vec) PG_ATTD(float, 2, true);
     if (vdim <= 64) PG_ATTD(float, 1, false);
     if (vdim <= 128) PG_ATTD(float, 2, false);
-    PG_ATTD(float, 4, false);
+    if (vdim <= 256) PG_ATTD(float, 4, false);
+    PG_ATTD(float, 8, false);
   }
   if (vec && vdim <= 64) PG_ATTD(bf16, 1, true);
   if (vec) PG_ATTD(bf16, 2, true);
   if (vdim <= 64) PG_ATTD(bf16, 1, false);
   if (vdim <= 128) PG_ATTD(bf16, 2, false);
-  PG_ATTD(bf16, 4, false);
+  if (vdim <= 256) PG_ATTD(bf16, 4, false);
+  PG_ATTD(bf16, 8, false);
 #undef PG_ATTD
 }

@@ -1,0 +1,311 @@
+// Routed feed-forward (mixture of experts) of the token-sequence decoders, without a host round trip: the step may sit in a
+// CUDA graph, so counts, offsets and tile lists stay on the device.
+//
+//   pg_moe_route     per token: softmax over the router outputs, choice score = probability + correction, optional group limit
+//                    (experts in `group_count` equal runs of neighbours; only the `group_keep` runs with the largest best
+//                    choice score stay eligible), the `top` largest choice scores, weights = chosen probabilities / their sum
+//                    * scale.  Outputs >= n_real are identity experts.  Counts the (token, choice) pairs of every real expert.
+//   pg_moe_plan      one CTA: expert offsets (exclusive scan), the list of row tiles (expert, first row, rows) and its length
+//   pg_moe_scatter   pair -> its row in the expert-sorted order (and back)
+//   pg_moe_gemm      out[row, f] = act(sum_k x[src(row), k] w[expert(row)][f, k]) over the tile list; plain fp32 FMAs
+//   pg_moe_combine   y[t] = sum_k weight[t, k] * (identity ? h[t] : expert_out[row(t, k)]) (+ shared[t])
+//
+// Router arithmetic, weights and the combine are fp32.
+#include "common.cuh"
+#include "paligemma_b200.h"
+
+using bf16 = __nv_bfloat16;
+
+#define PG_ST(s) reinterpret_cast<cudaStream_t>(s)
+#define PG_RET()                                                    \
+  do {                                                              \
+    pg_count_launch(1);                                             \
+    return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA; \
+  } while (0)
+
+namespace {
+
+constexpr int MOE_TILE = 32;  // rows of one expert per GEMM tile
+
+template <typename T>
+__device__ __forceinline__ float ldm(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ldm<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldm<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void stm(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void stm(bf16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float wmaxf(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float wsumf(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// (value, index) of the largest value in the warp, lowest index among equals
+__device__ __forceinline__ void wargmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+// One warp per token; probabilities and choice scores of the token in shared memory (2 * n_all floats per warp).
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
+                                                        int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T,
+                                                        int n_all, int n_real, int top, int group_count, int group_keep, float scale) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  float* prob = sm + (size_t)warp * 2 * n_all;
+  float* choice = prob + n_all;
+  const float* z = logits + (long long)t * ld;
+  float m = -INFINITY;
+  for (int i = lane; i < n_all; i += 32) m = fmaxf(m, z[i]);
+  m = wmaxf(m);
+  float s = 0.f;
+  for (int i = lane; i < n_all; i += 32) { const float e = expf(z[i] - m); prob[i] = e; s += e; }
+  s = wsumf(s);
+  for (int i = lane; i < n_all; i += 32) {
+    const float p = prob[i] / s;
+    prob[i] = p;
+    choice[i] = p + (correction != nullptr ? correction[i] : 0.f);
+  }
+  __syncwarp();
+  if (group_count > 1 && group_keep < group_count) {
+    // lane <-> group (rounds of 32): best choice score of the group; the kept groups are marked by negating nothing -- the
+    // dropped ones get -inf choice scores afterwards
+    const int per = n_all / group_count;
+    // group scores into registers of the owning lanes (group g -> lane g % 32, slot g / 32); up to 8 slots = 256 groups
+    float gs[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int g = lane + 32 * k;
+      float b = -INFINITY;
+      if (g < group_count)
+        for (int i = 0; i < per; ++i) b = fmaxf(b, choice[g * per + i]);
+      gs[k] = b;
+    }
+    unsigned keepmask[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // bit `lane` of slot k, only meaningful in the owning lane
+    for (int r = 0; r < group_keep; ++r) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int g = lane + 32 * k;
+        if (g < group_count && !(keepmask[k] & 1u) && (gs[k] > bv || (gs[k] == bv && g < bi))) { bv = gs[k]; bi = g; }
+      }
+      wargmax(bv, bi);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (bi == lane + 32 * k) keepmask[k] |= 1u;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int g = lane + 32 * k;
+      if (g < group_count && !(keepmask[k] & 1u))
+        for (int i = 0; i < per; ++i) choice[g * per + i] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float wsum_sel = 0.f;
+  int my_id = -1;
+  float my_p = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < n_all; i += 32) {
+      const float c = choice[i];
+      if (c > bv || (c == bv && i < bi)) { bv = c; bi = i; }
+    }
+    wargmax(bv, bi);
+    if (bi >= n_all) bi = 0;  // every score -inf / NaN: never with finite inputs
+    const float p = prob[bi];
+    wsum_sel += p;
+    if (lane == (r & 31)) { my_id = bi; my_p = p; }
+    if (lane == 0) choice[bi] = -INFINITY;
+    __syncwarp();
+    if ((r & 31) == 31 || r == top - 1) {  // flush up to 32 choices
+      const int base = r & ~31;
+      if (my_id >= 0) {
+        ids[(long long)t * top + base + lane] = my_id;
+        weights[(long long)t * top + base + lane] = my_p;  // normalised below
+        if (my_id < n_real) atomicAdd(counts + my_id, 1);
+      }
+      my_id = -1;
+    }
+  }
+  __syncwarp();
+  const float f = scale / (wsum_sel + 1e-20f);
+  for (int r = lane; r < top; r += 32) weights[(long long)t * top + r] *= f;
+}
+
+// counts -> offsets, tile list.  plan[0] = number of tiles; tiles: (expert, first sorted row, rows) triples from plan[4].
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ fill, int* __restrict__ plan, int n_real,
+                                int max_tiles) {
+  if (threadIdx.x != 0) return;
+  int off = 0, nt = 0;
+  for (int e = 0; e < n_real; ++e) {
+    const int c = counts[e];
+    offsets[e] = off;
+    fill[e] = 0;
+    for (int r = 0; r < c; r += MOE_TILE) {
+      if (nt < max_tiles) {
+        plan[4 + 3 * nt] = e;
+        plan[4 + 3 * nt + 1] = off + r;
+        plan[4 + 3 * nt + 2] = min(MOE_TILE, c - r);
+      }
+      ++nt;
+    }
+    off += c;
+  }
+  offsets[n_real] = off;
+  plan[0] = nt < max_tiles ? nt : max_tiles;
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ offsets, int* __restrict__ fill, int* __restrict__ sorted_pair,
+                                   int* __restrict__ pair_row, int pairs, int n_real) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= pairs) return;
+  const int e = ids[p];
+  if (e >= n_real) { pair_row[p] = -1; return; }
+  const int row = offsets[e] + atomicAdd(fill + e, 1);
+  sorted_pair[row] = p;
+  pair_row[p] = row;
+}
+
+// Tile = up to 32 sorted rows of one expert x 64 features; 256 threads, thread = 2 rows x 4 features.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
+                                                       const TI* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
+                                                       long long ldo, const int* __restrict__ plan, int F, int K, int act) {
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
+  const int f0 = blockIdx.x * 64;
+  __shared__ float xs[16][MOE_TILE + 4];
+  __shared__ float ws[16][64 + 4];
+  __shared__ long long src[MOE_TILE];
+  if (threadIdx.x < MOE_TILE) {
+    long long s = -1;
+    if (threadIdx.x < nr) s = src_div > 0 ? sorted_pair[r0 + threadIdx.x] / src_div : (long long)(r0 + threadIdx.x);
+    src[threadIdx.x] = s;
+  }
+  __syncthreads();
+  const TI* we = w + (long long)e * expert_stride;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // features 4 tx .. + 4, rows 2 ty .. + 2
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < MOE_TILE * 16; i += 256) {
+      const int r = i >> 4, k = i & 15;
+      xs[k][r] = (src[r] >= 0 && k0 + k < K) ? ldm(x, src[r] * ldx + k0 + k) : 0.f;
+    }
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int r = i >> 4, k = i & 15;
+      ws[k][r] = (f0 + r < F && k0 + k < K) ? ldm(we, (long long)(f0 + r) * ldw + k0 + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float a0 = xs[k][2 * ty], a1 = xs[k][2 * ty + 1];
+      const float4 b = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
+      acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]); acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
+      acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]); acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = 2 * ty + i, f = f0 + tx * 4 + j;
+      if (r < nr && f < F) {
+        float v = acc[i][j];
+        if (act == 2) { v = fmaxf(v, 0.f); v *= v; }
+        stm(out, (long long)(r0 + r) * ldo + f, v);
+      }
+    }
+}
+
+template <typename TA>
+__global__ void moe_combine_kernel(const float* __restrict__ expert_out, long long ldy, const int* __restrict__ pair_row, const int* __restrict__ ids,
+                                   const float* __restrict__ weights, const TA* __restrict__ h, long long ldh, const float* __restrict__ shared_out,
+                                   long long lds, float* __restrict__ y, int D, int top) {
+  const long long t = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = pair_row[t * top + k];
+      const float wgt = weights[t * top + k];
+      const float v = row < 0 ? ldm(h, t * ldh + d) : expert_out[(long long)row * ldy + d];
+      acc = fmaf(wgt, v, acc);
+    }
+    if (shared_out != nullptr) acc += shared_out[t * lds + d];
+    y[t * D + d] = acc;
+  }
+}
+
+}  // namespace
+
+extern "C" int pg_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int* counts, int tokens, int n_all,
+                            int n_real, int top, int group_count, int group_keep, float scale, void* stream) {
+  if (tokens <= 0 || n_all <= 0 || n_real < 0 || n_real > n_all || top <= 0 || top > n_all) return PG_ERR_ARG;
+  if (group_count > 1 && (n_all % group_count != 0 || group_keep <= 0 || group_keep > group_count || group_count > 256)) return PG_ERR_ARG;
+  if (group_count > 1 && top > (long long)group_keep * (n_all / group_count)) return PG_ERR_ARG;
+  const size_t smem = (size_t)4 * 2 * n_all * sizeof(float);
+  if (smem > 48 * 1024) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (n_real > 0 && cudaMemsetAsync(counts, 0, (size_t)n_real * sizeof(int), st) != cudaSuccess) return PG_ERR_CUDA;
+  moe_route_kernel<<<(tokens + 3) / 4, 128, smem, st>>>(logits, ld, correction, ids, weights, counts, tokens, n_all, n_real, top, group_count, group_keep,
+                                                        scale);
+  PG_RET();
+}
+
+extern "C" int pg_moe_tile_rows(void) { return MOE_TILE; }
+
+extern "C" int pg_moe_plan(const int* counts, const int* ids, int* offsets, int* fill, int* plan, int* sorted_pair, int* pair_row, int pairs,
+                           int n_real, int max_tiles, void* stream) {
+  if (pairs <= 0 || n_real <= 0 || max_tiles <= 0) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  moe_plan_kernel<<<1, 32, 0, st>>>(counts, offsets, fill, plan, n_real, max_tiles);
+  pg_count_launch(1);
+  moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(ids, offsets, fill, sorted_pair, pair_row, pairs, n_real);
+  PG_RET();
+}
+
+extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
+                           void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, void* stream) {
+  if (max_tiles <= 0 || max_tiles > 65535 || F <= 0 || K <= 0 || src_div < 0) return PG_ERR_ARG;
+  dim3 grid((F + 63) / 64, max_tiles);
+  cudaStream_t st = PG_ST(stream);
+  if (in_f32 && out_f32)
+    moe_gemm_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, sorted_pair, src_div, static_cast<const float*>(w), expert_stride,
+                                                       ldw, static_cast<float*>(out), ldo, plan, F, K, act);
+  else if (!in_f32 && out_f32)
+    moe_gemm_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride,
+                                                      ldw, static_cast<float*>(out), ldo, plan, F, K, act);
+  else if (!in_f32 && !out_f32)
+    moe_gemm_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride,
+                                                     ldw, static_cast<bf16*>(out), ldo, plan, F, K, act);
+  else
+    return PG_ERR_ARG;
+  PG_RET();
+}
+
+extern "C" int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
+                              long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream) {
+  if (tokens <= 0 || D <= 0 || top <= 0) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (act_f32)
+    moe_combine_kernel<float><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const float*>(h), ldh, shared_out, lds, y, D, top);
+  else
+    moe_combine_kernel<bf16><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const bf16*>(h), ldh, shared_out, lds, y, D, top);
+  PG_RET();
+}

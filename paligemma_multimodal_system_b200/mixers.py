@@ -166,3 +166,160 @@ class TokenSideInput:
         gz = prec.empty(T, self.n_pad)
         seq_ops.side_gate(z, b.tokens, table, self.index * self.n, gz, self.n)
         return seq_ops.linear(gz, self.w_proj, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class LatentAttention:
+    """Attention whose keys and values are linear images of one cached low-rank row per token.
+
+        [c_q | c | r] = W_in h;  c_q <- rms(c_q) w_q;  c <- rms(c) w_c;  r <- rotate(r, position)       (cache row: [c | r])
+        q_h = W_uq,h c_q = [q_plain | q_rot],  q_rot <- rotate(q_rot, position)
+        score(i, j) = (q_plain,h(i) . W_uk,h c(j) + q_rot,h(i) . r(j)) * scale,  out_h = sigmoid(g_h) * sum_j p(i, j) W_uv,h c(j)
+
+    The step computes it in the absorbed form -- (W_uk,h^T q_plain,h) . c(j), and W_uv,h applied after the weighted sum of the
+    c(j) -- so the paged cache is read as ONE key/value head of width rank + rot (values = its first `rank` columns) shared by
+    all query heads, and nothing per head is ever stored.  Prompt portions in bf16 whose head sizes the tensor-core kernel is
+    built for use the explicit-head form instead: keys / values of the entry's tokens are rebuilt from the cached rows into
+    scratch pages (the products are 3 .. 5 times smaller there)."""
+
+    def __init__(self, width, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, rot_dims, rot_base, eps):
+        if rot_dims % 2 or rot_dims > rot_dim:
+            raise ValueError("rotary dimensions must be even and at most the rotated key part")
+        self.D, self.H, self.dim, self.rot, self.vdim, self.Q, self.R = width, heads, dim, rot_dim, vdim, q_rank, kv_rank
+        self.scale, self.rot_dims, self.eps = float(scale), int(rot_dims), float(eps)
+        self.freq = rotary_frequencies(rot_base, rot_dims) if rot_dims else torch.zeros(1, dtype=torch.float64)
+        self.explicit_prefill = False
+
+    def cache_spec(self):
+        return ("latent", self.R + self.rot)
+
+    def load(self, take, pre):
+        H, dim, rot, vdim, Q, R, D = self.H, self.dim, self.rot, self.vdim, self.Q, self.R, self.D
+        self.w = dict(dq=take(pre + "dq", (Q, D)), qn=take(pre + "dq.norm", (Q,)), uq=take(pre + "uq", (H * (dim + rot), Q)),
+                      dkv=take(pre + "dkv", (R + rot, D)), cn=take(pre + "dkv.norm", (R,)), uk=take(pre + "uk", (H * dim, R)),
+                      uv=take(pre + "uv", (H * vdim, R)), g=take(pre + "g", (H, D)), o=take(pre + "o", (D, H * vdim)))
+
+    def pack(self, prec):
+        w, H, dim, vdim, R = self.w, self.H, self.dim, self.vdim, self.R
+        dev = dict(device="cuda", dtype=prec.dtype)
+        self.w_in = torch.cat([w["dq"], w["dkv"], w["g"]], 0).to(**dev).contiguous()
+        self.w_uq = w["uq"].to(**dev).contiguous()
+        self.w_ukT = w["uk"].to(**dev).view(H, dim, R).transpose(1, 2).contiguous()   # [H, R, dim]: q_plain -> latent space
+        self.w_uv = w["uv"].to(**dev).view(H, vdim, R).contiguous()
+        self.w_ukv = torch.cat([w["uk"], w["uv"]], 0).to(**dev).contiguous()            # explicit-head form
+        self.w_o = w["o"].to(**dev).contiguous()
+        self.qn, self.cn = w["qn"].to("cuda", torch.float32), w["cn"].to("cuda", torch.float32)
+        self.freq_d = self.freq.to("cuda")
+
+    def __call__(self, h, b, store, li, prec):
+        H, dim, rot, vdim, Q, R = self.H, self.dim, self.rot, self.vdim, self.Q, self.R
+        T, kd = b.T, R + rot
+        pages = store.k_pages[li]
+        proj = seq_ops.linear(h, self.w_in, prec.empty(T, self.w_in.shape[0]))
+        cq = prec.empty(T, Q)
+        seq_ops.latent_prepare(proj, b, self.freq_d, self.qn, self.cn, cq, pages, Q, R, rot, self.rot_dims, self.eps, PAGE)
+        q = seq_ops.linear(cq, self.w_uq, prec.empty(T, H * (dim + rot))).view(T, H, dim + rot)
+        gate = proj[:, Q + R + rot:]
+        att = prec.empty(T, H, vdim)
+        explicit = (self.explicit_prefill and not prec.f32 and b.singles < b.E and (dim + rot, vdim) in seq_ops.MMA_HEAD_SIZES
+                    and R % 8 == 0 and (dim + rot) % 8 == 0)
+        if explicit:
+            self._explicit(q, gate, att, b, pages, prec)
+        if not explicit or b.singles:
+            qlat = prec.empty(T, H, kd)
+            seq_ops.linear_batched(q[:, :, :dim], self.w_ukT, qlat[:, :, :R])
+            seq_ops.rotate_heads(q[:, :, dim:], qlat[:, :, R:], b.pos, self.freq_d, self.rot_dims)
+            olat = prec.empty(T, H, R)
+            seq_ops.attn_ragged(qlat.view(T, H * kd), pages, pages, gate, olat.view(T, H * R), b, H, 1, kd, R, self.scale, 0.0, PAGE,
+                                krow=kd, vrow=kd, gate_per_head=True, only_singles=explicit)
+            if explicit:
+                # rows of single-token entries only: the explicit form has written the others
+                seq_ops.linear_batched_rows(olat, self.w_uv, att, b.single_rows)
+            else:
+                seq_ops.linear_batched(olat, self.w_uv, att)
+        return seq_ops.linear(att.view(T, H * vdim), self.w_o, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+    def _explicit(self, q, gate, att, b, pages, prec):
+        raise NotImplementedError
+
+
+class SquaredReluFeedForward:
+    """W_down relu(W_up h)^2."""
+
+    def __init__(self, width, ff):
+        self.D, self.F = width, ff
+
+    def load(self, take, pre):
+        self.w = dict(up=take(pre + "up", (self.F, self.D)), down=take(pre + "down", (self.D, self.F)))
+
+    def pack(self, prec):
+        self.w_up = self.w["up"].to("cuda", prec.dtype).contiguous()
+        self.w_down = self.w["down"].to("cuda", prec.dtype).contiguous()
+
+    def __call__(self, h, b, prec):
+        T = h.shape[0]
+        mid = seq_ops.linear(h, self.w_up, prec.empty(T, self.F), act=seq_ops.ACT_RELU2)
+        return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class RoutedFeedForward:
+    """Mixture of squared-relu experts.  Router: p = softmax(W_r h) in fp32 over `experts + identity` outputs; the choice uses
+    p + correction, limited to the `group_keep` best of `group_count` runs of neighbouring outputs; the `top` chosen outputs
+    weigh in with p / sum(p chosen) * scale.  The last `identity` outputs return h itself.  A shared expert (optional) is added
+    for every token."""
+
+    def __init__(self, width, experts, identity, top, group_count, group_keep, scale, expert_ff, shared_ff):
+        self.D, self.n_real, self.n_all, self.top = width, int(experts), int(experts) + int(identity), int(top)
+        self.group_count, self.group_keep, self.scale, self.F = int(group_count), int(group_keep), float(scale), int(expert_ff)
+        if self.group_count > 1 and self.n_all % self.group_count:
+            raise ValueError("router outputs must divide into equal groups")
+        self.shared = SquaredReluFeedForward(width, int(shared_ff)) if shared_ff else None
+
+    def load(self, take, pre):
+        D, F = self.D, self.F
+        self.w = dict(router=take(pre + "router", (self.n_all, D)), correction=take(pre + "correction", (self.n_all,)),
+                      up=[take(f"{pre}e{e}.up", (F, D)) for e in range(self.n_real)], down=[take(f"{pre}e{e}.down", (D, F)) for e in range(self.n_real)])
+        if self.shared is not None:
+            self.shared.load(take, pre + "shared.")
+
+    def pack(self, prec):
+        w = self.w
+        self.w_router = w["router"].to("cuda", prec.dtype).contiguous()
+        self.correction = w["correction"].to("cuda", torch.float32).contiguous()
+        if self.n_real:
+            self.w_up = torch.stack(w["up"]).to("cuda", prec.dtype).contiguous()
+            self.w_down = torch.stack(w["down"]).to("cuda", prec.dtype).contiguous()
+        if self.shared is not None:
+            self.shared.pack(prec)
+
+    def __call__(self, h, b, prec):
+        T = h.shape[0]
+        z = seq_ops.linear(h, self.w_router, torch.empty(T, self.n_all, device="cuda", dtype=torch.float32))
+        ids, wts, counts = seq_ops.moe_route(z, self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
+        plan = seq_ops.MoePlan(ids, counts, max(1, self.n_real))
+        eo = None
+        if self.n_real:
+            mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_RELU2)
+            eo = seq_ops.moe_gemm(mid, plan, self.w_down, torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32), gather=False)
+        sh = self.shared(h, b, prec) if self.shared is not None else None
+        return seq_ops.moe_combine(eo, plan, ids, wts, h, sh, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class StreamCoefficients:
+    """Read vector a [S], write vector b [S] and mixing matrix M [S from, S to] of one sub-layer over a multi-stream residual:
+    the sub-layer reads sum_s a_s x_s and every stream becomes sum_s M[s, t] x_s + b_t y.  `plain(S)` is the ordinary residual
+    sum (one stream, all ones)."""
+
+    def __init__(self, S):
+        self.S = S
+        self.w = None
+
+    def load(self, take, pre):
+        S = self.S
+        self.w = dict(read=take(pre + "in", (S,)), write=take(pre + "out", (S,)), mix=take(pre + "mix", (S, S)))
+
+    def pack(self):
+        f32 = dict(device="cuda", dtype=torch.float32)
+        if self.w is None:
+            self.read, self.write, self.mix = torch.ones(self.S, **f32), torch.ones(self.S, **f32), torch.eye(self.S, **f32)
+        else:
+            self.read, self.write, self.mix = (self.w[k].to(**f32).contiguous() for k in ("read", "write", "mix"))

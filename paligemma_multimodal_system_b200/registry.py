@@ -53,6 +53,12 @@ def _load_mapedra(path, dtype=torch.bfloat16, **kw):
     return load_mapedra(path, dtype)
 
 
+def _load_pukerax(path, dtype=torch.bfloat16, **kw):
+    from .modeling_pukerax import load_pukerax
+    return load_pukerax(path, dtype)
+
+
 for _n in ("paligemma", "PaliGemmaForConditionalGeneration"):
     register(_n, _load_paligemma)
 register("Mapedra", _load_mapedra)
+register("Pukerax", _load_pukerax)

@@ -112,15 +112,22 @@ def _aligned(t, n=16):
     return t.data_ptr() % n == 0
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
-    """out[t, f] = sum_k x[t, k] w[f, k].  x, w share a type (bf16 / fp32); out is bf16 or fp32.  bf16 operands go to the
-    tcgen05 kernel when TMA can describe them (16-byte pitches and bases), everything else to the plain-FMA kernel."""
+ACT_NONE, ACT_GELU, ACT_RELU2 = 0, 1, 2
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_NONE):
+    """out[t, f] = act(sum_k x[t, k] w[f, k]).  x, w share a type (bf16 / fp32); out is bf16 or fp32.  bf16 operands go to the
+    tcgen05 kernel when TMA can describe them (16-byte pitches and bases), everything else to the plain-FMA kernel.
+    act = ACT_RELU2 (relu squared; out in the operands' type): in the tensor-core kernel's bf16 epilogue, else a pass of its own."""
     T, K = x.shape
     F = w.shape[0]
     assert x.dtype == w.dtype and w.shape[1] == K and out.shape[0] == T and out.shape[1] == F
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and F % 8 == 0
             and out.stride(0) % 8 == 0 and _aligned(x) and _aligned(w) and _aligned(out)):
+        assert act == ACT_NONE or out.dtype == torch.bfloat16
+        if act != ACT_NONE:
+            return _lib.gemm(x, w, out, mode=_lib.EPI_BF16, act_gelu=act, swap=1 if T <= 128 else 0)
         if T <= 128 and out.dtype == torch.float32:
             # few rows, few 128-feature tiles (output and down projections): split K over CTAs so that the whole GPU streams the
             # weights; the fp32 partials are red.add-ed into the zeroed output (as the framework's other decode GEMMs do)
@@ -134,6 +141,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
         raise ValueError("fp32 operands produce fp32 outputs")
     _lib.check(_lib.lib().pg_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), T, F, K,
                                        int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt")
+    if act == ACT_RELU2:
+        _lib.check(_lib.lib().pg_relu2(out.data_ptr(), out.stride(0), T, F, int(out.dtype == torch.float32), _lib.stream()), "pg_relu2")
+    elif act != ACT_NONE:
+        raise ValueError("the plain-FMA product has no fused activation but relu squared")
     return out
 
 
@@ -185,25 +196,34 @@ def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_page
 
 
 # head sizes (dim, vdim) the tensor-core attention kernel is instantiated for
-MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64)}
+MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64), (192, 128)}
 
 
-def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True):
+def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True,
+                krow=0, vrow=0, gate_per_head=False, only_singles=False):
     """Entries with several new rows go to a tiled kernel -- on the tensor cores for bf16 activations and the usual head
     sizes (fp32 probabilities as three bf16 terms), plain fp32 FMAs otherwise -- and entries with ONE new row (decoded tokens)
     to the key-split kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation
-    order."""
+    order.  krow / vrow: elements per cache row when it is not G * dim / G * vdim (a latent cache: one row is key and value);
+    gate_per_head: the gate holds one scalar per head instead of one per output element; only_singles: rows of entries with
+    several new tokens are left alone (another form computes them)."""
     L, f32 = _lib.lib(), int(q.dtype == torch.float32)
     ldg = 0 if gate is None else gate.stride(0)
+    gph = int(bool(gate_per_head))
     singles = b.singles if decode_kernel else 0
-    if singles < b.E and tensor_cores and not f32 and (dim, vdim) in MMA_HEAD_SIZES and ldg % 2 == 0 and (gate is None or gate.data_ptr() % 4 == 0):
+    dense_rows = krow in (0, G * dim) and vrow in (0, G * vdim)
+    if only_singles:
+        pass
+    elif (singles < b.E and tensor_cores and not f32 and dense_rows and (dim, vdim) in MMA_HEAD_SIZES
+            and (gate is None or gph or (ldg % 2 == 0 and gate.data_ptr() % 4 == 0))):
         _lib.check(L.pg_attn_ragged_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
                                         b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
-                                        float(scale), float(softcap or 0.0), int(singles > 0), _lib.stream()), "pg_attn_ragged_mma")
+                                        float(scale), float(softcap or 0.0), int(singles > 0), gph, _lib.stream()), "pg_attn_ragged_mma")
     elif singles < b.E:
         _lib.check(L.pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
                                     b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
-                                    float(scale), float(softcap or 0.0), int(singles > 0), f32, _lib.stream()), "pg_attn_ragged")
+                                    float(scale), float(softcap or 0.0), int(singles > 0), f32, int(krow), int(vrow), gph, _lib.stream()),
+                   "pg_attn_ragged")
     if singles:
         tiles = b.max_single_ctx // 32 + 1
         # enough CTAs for two waves, but at least two 32-key tiles for every warp of a CTA
@@ -211,7 +231,115 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
         partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
         _lib.check(L.pg_attn_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial),
                                     b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit,
-                                    H, G, dim, vdim, float(scale), float(softcap or 0.0), f32, _lib.stream()), "pg_attn_decode")
+                                    H, G, dim, vdim, float(scale), float(softcap or 0.0), f32, int(krow), int(vrow), gph, _lib.stream()),
+                   "pg_attn_decode")
+
+
+# ---- multi-stream residual -------------------------------------------------------------------------------------------
+def embed_streams(tokens, table, S, D, scale=1.0):
+    xs = torch.empty(tokens.numel(), S, D, device="cuda", dtype=torch.float32)
+    _lib.check(_lib.lib().pg_embed_streams(tokens.data_ptr(), table.data_ptr(), table.stride(0), xs.data_ptr(), tokens.numel(), S, D, float(scale),
+                                           int(table.dtype == torch.float32), _lib.stream()), "pg_embed_streams")
+    return xs
+
+
+def stream_mix_norm(xs, y=None, mix=None, write=None, read=None, norm_w=None, out_act=None, eps=1e-6):
+    """One pass over the stream rows xs [T, S, D] (fp32, in place): the write-back of a finished sub-layer (y fp32 [T, D], mix
+    [S, S] from x to, write [S]) and / or the normalised read of the next one (read [S], norm_w [D] -> out_act [T, D])."""
+    T, S, D = xs.shape
+    assert xs.dtype == torch.float32 and xs.is_contiguous()
+    assert y is None or (y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (T, D))
+    for t in (mix, write, read, norm_w):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert out_act is None or (out_act.is_contiguous() and out_act.shape == (T, D))
+    _lib.check(_lib.lib().pg_stream_mix_norm(xs.data_ptr(), _lib.ptr(y), 0 if y is None else y.stride(0), _lib.ptr(mix), _lib.ptr(write), _lib.ptr(read),
+                                             _lib.ptr(norm_w), _lib.ptr(out_act), T, S, D, float(eps),
+                                             int(out_act is not None and out_act.dtype == torch.float32), _lib.stream()), "pg_stream_mix_norm")
+    return out_act
+
+
+# ---- latent attention ------------------------------------------------------------------------------------------------
+def linear_batched(x, w, out):
+    """out[:, b, :] = x[:, b, :] @ w[b].T for every b: x [T, B, K] and out [T, B, F] are views with unit last stride, w [B, F, K].
+    Plain fp32 FMAs (bf16 or fp32 operands)."""
+    T, B, K = x.shape
+    F = w.shape[1]
+    assert w.shape == (B, F, K) and out.shape == (T, B, F) and x.dtype == w.dtype and w.is_contiguous()
+    assert x.stride(2) == 1 and out.stride(2) == 1
+    _lib.check(_lib.lib().pg_gemm_simt_batched(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), K, F * K, out.data_ptr(), out.stride(0),
+                                               out.stride(1), T, F, K, B, int(x.dtype == torch.float32), int(out.dtype == torch.float32),
+                                               _lib.stream()), "pg_gemm_simt_batched")
+    return out
+
+
+def latent_prepare(proj, b: StepBatch, freq, q_norm, c_norm, cq_out, pages, q_rank, rank, rot, rot_dims, eps, page):
+    assert proj.stride(1) == 1 and freq.dtype == torch.float64 and pages.dtype == proj.dtype and pages.shape[-1] == rank + rot
+    assert cq_out is None or (cq_out.dtype == proj.dtype and cq_out.is_contiguous())
+    _lib.check(_lib.lib().pg_latent_prepare(proj.data_ptr(), proj.stride(0), b.pos.data_ptr(), b.row_entry.data_ptr(), b.page_table.data_ptr(),
+                                            b.max_pages, page, freq.data_ptr(), _lib.ptr(q_norm), c_norm.data_ptr(), _lib.ptr(cq_out), pages.data_ptr(),
+                                            b.T, q_rank, rank, rot, rot_dims, float(eps), int(proj.dtype == torch.float32), _lib.stream()),
+               "pg_latent_prepare")
+
+
+def rotate_heads(src, dst, pos, freq, rot_dims):
+    """src, dst: [T, H, n] views (unit last stride, any row / head pitch) of one type; the first rot_dims of every head vector are
+    rotated in interleaved pairs by pos[t] * freq[i]."""
+    T, H, n = src.shape
+    assert dst.shape == src.shape and src.dtype == dst.dtype and src.stride(2) == 1 and dst.stride(2) == 1
+    _lib.check(_lib.lib().pg_rotate_heads(src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(), dst.stride(0), dst.stride(1), pos.data_ptr(),
+                                          freq.data_ptr(), T, H, n, rot_dims, int(src.dtype == torch.float32), _lib.stream()), "pg_rotate_heads")
+
+
+# ---- routed feed-forward ---------------------------------------------------------------------------------------------
+def moe_route(logits, correction, n_real, top, group_count, group_keep, scale):
+    """logits fp32 [T, n_all] -> ids int32 [T, top], weights fp32 [T, top], counts int32 [n_real] (device)."""
+    T, n_all = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    ids = torch.empty(T, top, device="cuda", dtype=torch.int32)
+    wts = torch.empty(T, top, device="cuda", dtype=torch.float32)
+    counts = torch.empty(max(1, n_real), device="cuda", dtype=torch.int32)
+    _lib.check(_lib.lib().pg_moe_route(logits.data_ptr(), logits.stride(0), _lib.ptr(correction), ids.data_ptr(), wts.data_ptr(), counts.data_ptr(), T,
+                                       n_all, n_real, top, int(group_count), int(group_keep), float(scale), _lib.stream()), "pg_moe_route")
+    return ids, wts, counts
+
+
+class MoePlan:
+    """Device-side order of the (token, choice) pairs by expert and the list of row tiles the grouped products walk."""
+
+    def __init__(self, ids, counts, n_real):
+        L = _lib.lib()
+        T, top = ids.shape
+        self.pairs, self.top = T * top, top
+        self.max_tiles = -(-self.pairs // L.pg_moe_tile_rows()) + n_real
+        i32 = dict(device="cuda", dtype=torch.int32)
+        self.offsets = torch.empty(n_real + 1, **i32)
+        self.fill = torch.empty(n_real, **i32)
+        self.plan = torch.empty(4 + 3 * self.max_tiles, **i32)
+        self.sorted_pair = torch.empty(self.pairs, **i32)
+        self.pair_row = torch.empty(self.pairs, **i32)
+        _lib.check(L.pg_moe_plan(counts.data_ptr(), ids.data_ptr(), self.offsets.data_ptr(), self.fill.data_ptr(), self.plan.data_ptr(),
+                                 self.sorted_pair.data_ptr(), self.pair_row.data_ptr(), self.pairs, n_real, self.max_tiles, _lib.stream()), "pg_moe_plan")
+
+
+def moe_gemm(x, plan: MoePlan, w, out, gather, act=0):
+    """out[row] = act(x[src(row)] @ w[expert(row)].T) over the plan's tiles; gather: x rows are tokens (src = pair // top),
+    else x rows are already in sorted order.  w [n_real, F, K] contiguous."""
+    n_real, F, K = w.shape
+    assert w.is_contiguous() and x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == K and out.shape[1] == F
+    _lib.check(_lib.lib().pg_moe_gemm(x.data_ptr(), x.stride(0), plan.sorted_pair.data_ptr(), plan.top if gather else 0, w.data_ptr(), F * K, K,
+                                      out.data_ptr(), out.stride(0), plan.plan.data_ptr(), plan.max_tiles, F, K, int(act),
+                                      int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_moe_gemm")
+    return out
+
+
+def moe_combine(expert_out, plan: MoePlan, ids, weights, h, shared_out, y):
+    T, D = y.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and h.stride(1) == 1
+    assert expert_out is None or (expert_out.dtype == torch.float32 and expert_out.stride(1) == 1)
+    _lib.check(_lib.lib().pg_moe_combine(_lib.ptr(expert_out), 0 if expert_out is None else expert_out.stride(0), plan.pair_row.data_ptr(), ids.data_ptr(),
+                                         weights.data_ptr(), h.data_ptr(), h.stride(0), _lib.ptr(shared_out), 0 if shared_out is None else shared_out.stride(0),
+                                         y.data_ptr(), T, D, plan.top, int(h.dtype == torch.float32), _lib.stream()), "pg_moe_combine")
+    return y
 
 
 # a portion at least this long is advanced in 32-token blocks; shorter ones (decode above all) token by token
