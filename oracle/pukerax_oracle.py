@@ -158,11 +158,13 @@ def tensor_shapes(cfg):
         sh.update({p + "norm1": (D,), p + "mix.dq": (Q, D), p + "mix.dq.norm": (Q,), p + "mix.uq": (H * (dim + rd), Q),
                    p + "mix.dkv": (R + rd, D), p + "mix.dkv.norm": (R,), p + "mix.uk": (H * dim, R), p + "mix.uv": (H * vd, R),
                    p + "mix.g": (H, D), p + "mix.o": (D, H * vd)})
-        sh.update({p + "hc1.in": (S,), p + "hc1.out": (S,), p + "hc1.mix": (S, S)})
+        if "streams" in cfg:
+            sh.update({p + "hc1.in": (S,), p + "hc1.out": (S,), p + "hc1.mix": (S, S)})
         mlp = l.get("mlp")
         if mlp:
             sh[p + "norm2"] = (D,)
-            sh.update({p + "hc2.in": (S,), p + "hc2.out": (S,), p + "hc2.mix": (S, S)})
+            if "streams" in cfg:
+                sh.update({p + "hc2.in": (S,), p + "hc2.out": (S,), p + "hc2.mix": (S, S)})
             if mlp["kind"] == "dense":
                 sh.update({p + "mlp.up": (int(mlp["ff"]), D), p + "mlp.down": (D, int(mlp["ff"]))})
             else:
