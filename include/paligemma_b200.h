@@ -381,6 +381,7 @@ int pg_stream_mix_norm(float* xs, const float* y, long long ldy, const float* mi
  * pg_rotate_heads: for every row and head, n elements at src[t * ld_src + h * head_stride_src ..] are copied to
  *   dst[t * ld_dst + h * head_stride_dst ..] with the first rot_dims rotated the same way.
  * pg_latent_gather: lat[dense_row0[e] + j, 0:rank] <- cached row j of entry e, j < ctx + n (width = elements per cache row).
+ *   Entries with n == 1 are skipped here and in pg_latent_pack_kv (they own no dense rows).
  * pg_latent_pack_kv: up[row] = [H x dim plain key parts | H x vdim values] (pitch ld_up) of the gathered rows ->
  *   k_out[row, h, :] = [plain (dim) | cached rotated part (rot)], v_out[row, h, :]. */
 int pg_latent_prepare(const void* proj, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,

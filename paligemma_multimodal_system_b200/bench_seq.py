@@ -250,3 +250,206 @@ def run(args):
             out[key] = round(out[key], 1)
     print(json.dumps(out), flush=True)
     return out
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# `bench.py --arch pukerax`: the Pukerax decoder beside the Mapedra decoder (the closest model of the package: same engine, same
+# ragged step, softmax attention over pages) at equal width / heads / feed-forward / depth
+# ----------------------------------------------------------------------------------------------------------------------
+def pukerax_config(width, heads, ff, vocab, layers, streams=4, experts=14, top=4):
+    """Latent attention with 64 plain + 32 rotated query / key dimensions per head, values of 64, a kv latent of 256 and a q
+    latent of 768; the first layer's feed-forward dense, the others routed (expert width ff / 8, shared expert ff / 4, two
+    identity outputs, four groups of which two are kept)."""
+    mixer = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 768, "rot": {"base": 1e6, "dims": 32}, "scale": 96 ** -0.5}
+    ls = []
+    for i in range(layers):
+        if i == 0:
+            mlp = {"kind": "dense", "ff": ff}
+        else:
+            mlp = {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 4},
+                   "router": {"experts": experts, "identity": 2, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+        ls.append({"type": "latent_attention", "mixer": dict(mixer), "mlp": mlp})
+    return {"architecture": "Pukerax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": streams, "layers": ls}
+
+
+def random_pukerax(cfg, seed=0):
+    from .modeling_pukerax import PukeraxConfig, PukeraxForCausalLM
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    c = PukeraxConfig(cfg)
+    model = PukeraxForCausalLM(c, torch.bfloat16)
+
+    def take(name, shape):
+        if name.endswith(("norm1", "norm2", "final.norm", "correction")):
+            t = torch.randn(*shape, device="cuda", generator=g) * 0.05
+        elif name.endswith(("dq.norm", "dkv.norm")):
+            t = 1.0 + torch.randn(*shape, device="cuda", generator=g) * 0.05
+        elif name.endswith(".in"):
+            t = torch.full(shape, 1.0 / c.streams, device="cuda")
+        elif name.endswith(".out"):
+            t = torch.ones(*shape, device="cuda")
+        elif name.endswith(".mix"):
+            t = torch.eye(shape[0], device="cuda") + 0.05 * torch.randn(*shape, device="cuda", generator=g)
+        else:
+            t = torch.randn(*shape, device="cuda", generator=g) * shape[-1] ** -0.5
+        return t.to(torch.bfloat16)
+
+    model.embed = take("embed", (c.vocab, c.width))
+    for blk in model.blocks:
+        blk.load(take)
+    model.final_norm, model.head = take("final.norm", (c.width,)), take("head", (c.vocab, c.width))
+    model.pack()
+    return model
+
+
+def _throughput(model, args, flush, V, tag, out):
+    B_pre, S, B_dec, ctx = args.prefill_batch, args.seq_len, args.decode_batch, args.context
+    eng = SequenceEngine(model, max_tokens=max(B_pre * S, B_dec * (ctx + PAGE)) + PAGE, num_slots=max(B_pre, B_dec))
+    gen = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, V, (S,), generator=gen).tolist() for _ in range(B_pre)]
+    t = timed(lambda: eng.step([(i, p, [S - 1]) for i, p in enumerate(prompts)], list(range(B_pre))), iters=args.steps, warmup=args.warmup, flush=flush)
+    out[f"{tag}_prefill_tok_s"] = B_pre * S / t
+    long = [torch.randint(0, V, (ctx,), generator=gen).tolist() for _ in range(B_dec)]
+    for i0 in range(0, B_dec, 8):
+        eng.step([(("d", i), long[i], []) for i in range(i0, min(B_dec, i0 + 8))])
+    t = timed(lambda: eng.step([(("d", i), [7], [0]) for i in range(B_dec)]), iters=max(args.steps, 8), warmup=args.warmup, flush=flush)
+    out[f"{tag}_decode_tok_s"] = B_dec / t
+    out[f"{tag}_decode_ms_per_step"] = t * 1e3
+    for i in range(B_dec):
+        eng.release(("d", i))
+    return eng
+
+
+def _entries(store, n_seq, n_new, c0):
+    es = []
+    for i in range(n_seq):
+        store.admit(("k", i))
+        rec = store.reserve(("k", i), c0 + n_new)
+        es.append(dict(tokens=[1] * n_new, ctx=c0, slot=rec.slot, pages=rec.pages))
+    return seq_ops.make_step_batch(es)
+
+
+def run_pukerax(args):
+    _lib.require_device()
+    torch.cuda.set_device(0)
+    hbm, tflops, src = peaks()
+    W, H, F, V, L = args.width, args.heads, args.ff, args.vocab, args.layers
+    B_pre, S, B_dec, ctx = args.prefill_batch, args.seq_len, args.decode_batch, args.context
+    flush = torch.zeros(64 * 1024 * 1024, device="cuda", dtype=torch.float32)  # 256 MB > L2
+    cfg = pukerax_config(W, H, F, V, L)
+    m0 = cfg["layers"][0]["mixer"]
+    out = {"metric": "pukerax_vs_mapedra_tokens_per_s", "dtype": "bf16", "data": "synthetic", "peaks": src,
+           "config": {"width": W, "heads": H, "latent": {k: m0[k] for k in ("dim", "rot_dim", "vdim", "kv_rank", "q_rank")}, "ff": F, "vocab": V,
+                      "layers": L, "streams": cfg["streams"], "router": cfg["layers"][-1]["mlp"]["router"] if L > 1 else None,
+                      "prefill": [B_pre, S], "decode": [B_dec, ctx], "l2": "256 MB buffer rewritten before every timed launch"}}
+    model = random_pukerax(cfg)
+    eng = _throughput(model, args, flush, V, "pukerax", out)
+
+    # ---------------------------------------------------------------- Pukerax kernels
+    prec, k, store = model.prec, {}, eng.store
+    mix = model.blocks[0].mixer
+    dim, rot, vdim, R, Q = mix.dim, mix.rot, mix.vdim, mix.R, mix.Q
+    kd = R + rot
+    Sn = cfg["streams"]
+    ff = next((b.ff for b in model.blocks if hasattr(b.ff, "n_real")), None)
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        pages = store.k_pages[0]
+        pages.normal_()
+        xs, y, ha = torch.randn(T, Sn, W, device="cuda"), torch.randn(T, W, device="cuda"), prec.empty(T, W)
+        hc, nw = model.blocks[0].hc1, model.blocks[0].norm1_d
+        k[f"stream_mix_norm_{name}"] = dict(s=timed(lambda: seq_ops.stream_mix_norm(xs, y, hc.mix, hc.write, read=hc.read, norm_w=nw, out_act=ha), flush=flush),
+                                            bytes=T * W * (2 * Sn * 4 + 4 + 2))
+        proj = torch.randn(T, mix.w_in.shape[0], device="cuda").to(torch.bfloat16)
+        cq = prec.empty(T, Q)
+        k[f"latent_prepare_{name}"] = dict(
+            s=timed(lambda: seq_ops.latent_prepare(proj, b, mix.freq_d, mix.qn, mix.cn, cq, pages, Q, R, rot, mix.rot_dims, 1e-6, PAGE), flush=flush),
+            bytes=T * (Q + kd) * 2 * 2)
+        q = torch.randn(T, H, dim + rot, device="cuda").to(torch.bfloat16)
+        gate = proj[:, Q + kd:]
+        att = prec.empty(T, H, vdim)
+        pairs = n_seq * (n_new * c0 + n_new * (n_new + 1) // 2)
+        if name == "prefill":
+            k["latent_expand_prefill"] = dict(s=timed(lambda: seq_ops.latent_expand(pages, b, mix.w_ukv, H, dim, rot, vdim, R, PAGE, prec), flush=flush),
+                                              flops=2 * T * R * H * (dim + vdim), bytes=T * (kd * 2 + 2 * H * (dim + vdim) * 2 + H * (dim + rot + vdim) * 2))
+            kx, vx = seq_ops.latent_expand(pages, b, mix.w_ukv, H, dim, rot, vdim, R, PAGE, prec)
+            k["attention_prefill"] = dict(
+                s=timed(lambda: seq_ops.attn_ragged(q.view(T, -1), kx, vx, gate, att.view(T, -1), seq_ops.dense_view(b), H, H, dim + rot, vdim, mix.scale, 0.0,
+                                                    PAGE, gate_per_head=True, skip_singles=True), flush=flush),
+                flops=2 * (dim + rot + vdim) * H * pairs, bytes=T * H * (2 * (dim + rot) + 2 * vdim) * 2)
+        else:
+            qlat, olat = prec.empty(T, H, kd), prec.empty(T, H, R)
+            k["absorb_query_decode"] = dict(s=timed(lambda: seq_ops.linear_batched(q[:, :, :dim], mix.w_ukT, qlat[:, :, :R]), flush=flush),
+                                            bytes=H * R * dim * 2 + T * H * (dim + R) * 2)
+            k["attention_decode"] = dict(
+                s=timed(lambda: seq_ops.attn_ragged(qlat.view(T, -1), pages, pages, gate, olat.view(T, -1), b, H, 1, kd, R, mix.scale, 0.0, PAGE, krow=kd, vrow=kd,
+                                                    gate_per_head=True), flush=flush),
+                flops=2 * (kd + R) * H * pairs, bytes=n_seq * (c0 + 1) * kd * 2 + T * H * (kd + R) * 2)
+            k["value_up_decode"] = dict(s=timed(lambda: seq_ops.linear_batched(olat, mix.w_uv, att), flush=flush), bytes=H * R * vdim * 2 + T * H * (vdim + R) * 2)
+        if ff is not None:
+            h = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+            z = torch.randn(T, ff.n_all, device="cuda")
+
+            def route():
+                ids, wts, counts = seq_ops.moe_route(z, ff.correction, ff.n_real, ff.top, ff.group_count, ff.group_keep, ff.scale)
+                return ids, wts, seq_ops.MoePlan(ids, counts, ff.n_real)
+
+            k[f"moe_route_plan_{name}"] = dict(s=timed(route, flush=flush), bytes=T * (ff.n_all * 4 + ff.top * 16))
+            ids, wts, plan = route()
+            real = int((ids < ff.n_real).sum())
+            mid, eo = prec.empty(plan.pairs, ff.F), torch.empty(plan.pairs, W, device="cuda", dtype=torch.float32)
+            wbytes = 2 * ff.n_real * ff.F * W * 2
+            k[f"moe_expert_products_{name}"] = dict(
+                s=timed(lambda: (seq_ops.moe_gemm(h, plan, ff.w_up, mid, gather=True, act=seq_ops.ACT_RELU2), seq_ops.moe_gemm(mid, plan, ff.w_down, eo, gather=False)),
+                        flush=flush), flops=4 * real * ff.F * W, bytes=wbytes + real * (W * 2 + ff.F * 4 + W * 4))
+            yy = torch.empty(T, W, device="cuda")
+            k[f"moe_combine_{name}"] = dict(s=timed(lambda: seq_ops.moe_combine(eo, plan, ids, wts, h, y, yy), flush=flush), bytes=T * W * (ff.top * 4 + 4 + 4 + 2))
+        for i in range(n_seq):
+            store.release(("k", i))
+    del eng, model, store
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- Mapedra (softmax attention on every layer) at equal size
+    mc = mapedra_config(W, H, 8, 64, F, V, L, every=1)
+    mm = random_mapedra(mc)
+    eng = _throughput(mm, args, flush, V, "mapedra", out)
+    store, prec = eng.store, mm.prec
+    att_m = mm.blocks[0].mixer
+    G, dh = att_m.G, att_m.dim
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        proj = torch.randn(T, att_m.w_in.shape[0], device="cuda").to(torch.bfloat16)
+        q, o = prec.empty(T, H * dh), prec.empty(T, H * dh)
+        kp, vp = store.k_pages[0], store.v_pages[0]
+        kp.normal_()
+        vp.normal_()
+        gate = proj[:, (H + G) * dh + G * dh:]
+        k[f"mapedra_attn_prepare_{name}"] = dict(
+            s=timed(lambda: seq_ops.attn_prepare(proj, b, att_m.freq_d, att_m.qn, att_m.kn, q, kp, vp, H, G, dh, dh, att_m.rot_dims, 1e-6, PAGE), flush=flush),
+            bytes=T * (H + 2 * G) * dh * 2 * 2)
+        pairs = n_seq * (n_new * c0 + n_new * (n_new + 1) // 2)
+        k[f"mapedra_attention_{name}"] = dict(
+            s=timed(lambda: seq_ops.attn_ragged(q, kp, vp, gate, o, b, H, G, dh, dh, att_m.scale, att_m.softcap, PAGE), flush=flush),
+            flops=4 * dh * H * pairs, bytes=n_seq * (c0 + n_new) * G * 2 * dh * 2 + 3 * T * H * dh * 2)
+        y, x, xa = torch.randn(T, W, device="cuda"), torch.randn(T, W, device="cuda"), prec.empty(T, W)
+        w1 = torch.ones(W, device="cuda")
+        k[f"mapedra_group_norm_residual_{name}"] = dict(s=timed(lambda: seq_ops.group_rmsnorm_add(y, w1, x, xa, 4, 1e-6), flush=flush), bytes=T * W * (4 + 4 + 4 + 2))
+        for i in range(n_seq):
+            store.release(("k", i))
+    for name, d in k.items():
+        d["us"] = round(d.pop("s") * 1e6, 2)
+        if "bytes" in d:
+            d["hbm_frac"] = round(d["bytes"] / (d["us"] * 1e-6) / hbm, 4)
+        if "flops" in d:
+            d["tflops"] = round(d["flops"] / (d["us"] * 1e-6) / 1e12, 2)
+            d["tensor_frac"] = round(d["flops"] / (d["us"] * 1e-6) / tflops, 5)
+    out["kernels"] = k
+    out["value"] = out["pukerax_decode_tok_s"]
+    out["unit"] = "tokens/s"
+    out["n_gpus"] = 1
+    for key in list(out):
+        if key.endswith("tok_s"):
+            out[key] = round(out[key], 1)
+    print(json.dumps(out), flush=True)
+    return out

@@ -6,8 +6,8 @@
 //                       pairwise rotation of the key part (-> the token's row in the cache pages)
 //   pg_rotate_heads     pairwise rotation of a slice of every head vector by the row's position, written to another layout
 //                       (q's rotated part into the absorbed query, or q / k as a whole)
-//   pg_latent_expand    keys / values of entries rebuilt from cached latents for the explicit-head form: gathers the latent rows
-//                       of every entry's context + new tokens into a dense matrix and notes each entry's first dense row
+//   pg_latent_gather    explicit-head form, step 1: the latent rows of every multi-token entry's context + new tokens are gathered
+//                       into a dense matrix (entry e from row dense_row0[e]), the operand of the key / value up projection
 //   pg_latent_pack_kv   [k_plain heads | v heads] of the up projection + the shared rotated part -> per-head key rows
 //                       [plain | rotated] and value rows in dense scratch "pages"
 //
@@ -123,6 +123,7 @@ __global__ void latent_gather_kernel(const TA* __restrict__ pages, const int* __
                                      const int* __restrict__ dense_row0, const int* __restrict__ entry_n, const int* __restrict__ entry_ctx,
                                      TA* __restrict__ lat, int rank, int width) {
   const int e = blockIdx.y;
+  if (entry_n[e] == 1) return;  // single-token entries are served by the absorbed form: they own no dense rows
   const int len = entry_ctx[e] + entry_n[e];
   for (int j = blockIdx.x; j < len; j += gridDim.x) {
     const TA* src = pages + ((long long)page_table[(long long)e * max_pages + j / page] * page + j % page) * width;
@@ -138,6 +139,7 @@ __global__ void latent_pack_kv_kernel(const TA* __restrict__ up, long long ld_up
                                       const int* __restrict__ entry_ctx, TA* __restrict__ k_out, TA* __restrict__ v_out, int H, int dim, int rot,
                                       int vdim, int rank) {
   const int e = blockIdx.y;
+  if (entry_n[e] == 1) return;
   const int len = entry_ctx[e] + entry_n[e];
   const int kd = dim + rot;
   for (int j = blockIdx.x; j < len; j += gridDim.x) {

@@ -7,7 +7,8 @@
 //                    * scale.  Outputs >= n_real are identity experts.  Counts the (token, choice) pairs of every real expert.
 //   pg_moe_plan      one CTA: expert offsets (exclusive scan), the list of row tiles (expert, first row, rows) and its length
 //   pg_moe_scatter   pair -> its row in the expert-sorted order (and back)
-//   pg_moe_gemm      out[row, f] = act(sum_k x[src(row), k] w[expert(row)][f, k]) over the tile list; plain fp32 FMAs
+//   pg_moe_gemm      out[row, f] = act(sum_k x[src(row), k] w[expert(row)][f, k]) over the tile list; plain fp32 FMAs, or
+//                    mma.sync on the tensor cores for bf16 operands
 //   pg_moe_combine   y[t] = sum_k weight[t, k] * (identity ? h[t] : expert_out[row(t, k)]) (+ shared[t])
 //
 // Router arithmetic, weights and the combine are fp32.
@@ -25,7 +26,7 @@ using bf16 = __nv_bfloat16;
 
 namespace {
 
-constexpr int MOE_TILE = 32;  // rows of one expert per GEMM tile
+constexpr int MOE_TILE = 64;  // rows of one expert per GEMM tile
 
 template <typename T>
 __device__ __forceinline__ float ldm(const T* p, long long i);
@@ -181,7 +182,7 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
   pair_row[p] = row;
 }
 
-// Tile = up to 32 sorted rows of one expert x 64 features; 256 threads, thread = 2 rows x 4 features.
+// Tile = up to 64 sorted rows of one expert x 64 features; 256 threads, thread = 4 rows x 4 features; plain fp32 FMAs in k order.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
                                                        const TI* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
@@ -200,8 +201,8 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x,
   }
   __syncthreads();
   const TI* we = w + (long long)e * expert_stride;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // features 4 tx .. + 4, rows 2 ty .. + 2
-  float acc[2][4] = {};
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // features 4 tx .. + 4, rows 4 ty .. + 4
+  float acc[4][4] = {};
   for (int k0 = 0; k0 < K; k0 += 16) {
     for (int i = threadIdx.x; i < MOE_TILE * 16; i += 256) {
       const int r = i >> 4, k = i & 15;
@@ -214,24 +215,128 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x,
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
-      const float a0 = xs[k][2 * ty], a1 = xs[k][2 * ty + 1];
+      const float4 a = *reinterpret_cast<const float4*>(&xs[k][ty * 4]);
       const float4 b = *reinterpret_cast<const float4*>(&ws[k][tx * 4]);
-      acc[0][0] = fmaf(a0, b.x, acc[0][0]); acc[0][1] = fmaf(a0, b.y, acc[0][1]); acc[0][2] = fmaf(a0, b.z, acc[0][2]); acc[0][3] = fmaf(a0, b.w, acc[0][3]);
-      acc[1][0] = fmaf(a1, b.x, acc[1][0]); acc[1][1] = fmaf(a1, b.y, acc[1][1]); acc[1][2] = fmaf(a1, b.z, acc[1][2]); acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int r = 2 * ty + i, f = f0 + tx * 4 + j;
+      const int r = 4 * ty + i, f = f0 + tx * 4 + j;
       if (r < nr && f < F) {
         float v = acc[i][j];
         if (act == 2) { v = fmaxf(v, 0.f); v *= v; }
         stm(out, (long long)(r0 + r) * ldo + f, v);
       }
     }
+}
+
+// The same product for bf16 operands on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tile = 64 sorted rows of one
+// expert x 128 features, 4 warps of 32 x 64, k in steps of 32 through shared memory; the next step's operands are fetched into
+// registers (16-byte loads; the x rows are gathered through the sorted order) while the current one is multiplied.
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
+                                                           const bf16* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
+                                                           long long ldo, const int* __restrict__ plan, int F, int K, int act) {
+  constexpr int LD = 40;  // bf16 elements per shared row: 32 + 8 (conflict-free fragment reads)
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
+  const int f0 = blockIdx.x * 128;
+  __shared__ __align__(16) bf16 As[MOE_TILE * LD];
+  __shared__ __align__(16) bf16 Bs[128 * LD];
+  __shared__ long long src[MOE_TILE];
+  if (threadIdx.x < MOE_TILE) {
+    long long s = -1;
+    if (threadIdx.x < nr) s = src_div > 0 ? sorted_pair[r0 + threadIdx.x] / src_div : (long long)(r0 + threadIdx.x);
+    src[threadIdx.x] = s;
+  }
+  __syncthreads();
+  const bf16* we = w + (long long)e * expert_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+  const int wm = warp >> 1, wn = warp & 1;
+  // this thread's 16-byte chunks of a k step: A chunks id = tid, tid + 128 (row id / 4, columns 8 (id % 4)); B chunks id = tid + 128 j
+  uint4 ra[2], rb[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int id = threadIdx.x + 128 * j, r = id >> 2, c = (id & 3) * 8;
+      ra[j] = make_uint4(0, 0, 0, 0);
+      if (src[r] >= 0 && k0 + c < K) ra[j] = *reinterpret_cast<const uint4*>(x + src[r] * ldx + k0 + c);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int id = threadIdx.x + 128 * j, r = id >> 2, c = (id & 3) * 8;
+      rb[j] = make_uint4(0, 0, 0, 0);
+      if (f0 + r < F && k0 + c < K) rb[j] = *reinterpret_cast<const uint4*>(we + (long long)(f0 + r) * ldw + k0 + c);
+    }
+  };
+  float acc[2][8][4];
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    __syncthreads();  // the previous step's fragments have been read
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int id = threadIdx.x + 128 * j;
+      *reinterpret_cast<uint4*>(As + (id >> 2) * LD + (id & 3) * 8) = ra[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int id = threadIdx.x + 128 * j;
+      *reinterpret_cast<uint4*>(Bs + (id >> 2) * LD + (id & 3) * 8) = rb[j];
+    }
+    __syncthreads();
+    if (k0 + 32 < K) fetch(k0 + 32);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        const bf16* ap = As + (32 * wm + 16 * mi + gq) * LD + ks * 16 + 2 * tq;
+        a[mi][0] = *reinterpret_cast<const uint32_t*>(ap);
+        a[mi][1] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD);
+        a[mi][2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+        a[mi][3] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD + 8);
+      }
+#pragma unroll
+      for (int ni = 0; ni < 8; ++ni) {
+        const bf16* bp = Bs + (64 * wn + 8 * ni + gq) * LD + ks * 16 + 2 * tq;
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp), b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
+        mma_bf16_16816(acc[0][ni], a[0], b0, b1);
+        mma_bf16_16816(acc[1][ni], a[1], b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 8; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = 32 * wm + 16 * mi + gq + ((c & 2) ? 8 : 0), f = f0 + 64 * wn + 8 * ni + 2 * tq + (c & 1);
+        if (r < nr && f < F) {
+          float v = acc[mi][ni][c];
+          if (act == 2) { v = fmaxf(v, 0.f); v *= v; }
+          stm(out, (long long)(r0 + r) * ldo + f, v);
+        }
+      }
 }
 
 template <typename TA>
@@ -285,6 +390,18 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
   if (max_tiles <= 0 || max_tiles > 65535 || F <= 0 || K <= 0 || src_div < 0) return PG_ERR_ARG;
   dim3 grid((F + 63) / 64, max_tiles);
   cudaStream_t st = PG_ST(stream);
+  // bf16 operands whose rows can be fetched in 16-byte pieces go to the tensor cores
+  if (!in_f32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
+    dim3 g2((F + 127) / 128, max_tiles);
+    if (out_f32)
+      moe_gemm_mma_kernel<float><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw,
+                                                    static_cast<float*>(out), ldo, plan, F, K, act);
+    else
+      moe_gemm_mma_kernel<bf16><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw,
+                                                   static_cast<bf16*>(out), ldo, plan, F, K, act);
+    PG_RET();
+  }
   if (in_f32 && out_f32)
     moe_gemm_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, sorted_pair, src_div, static_cast<const float*>(w), expert_stride,
                                                        ldw, static_cast<float*>(out), ldo, plan, F, K, act);

@@ -187,7 +187,7 @@ class LatentAttention:
         self.D, self.H, self.dim, self.rot, self.vdim, self.Q, self.R = width, heads, dim, rot_dim, vdim, q_rank, kv_rank
         self.scale, self.rot_dims, self.eps = float(scale), int(rot_dims), float(eps)
         self.freq = rotary_frequencies(rot_base, rot_dims) if rot_dims else torch.zeros(1, dtype=torch.float64)
-        self.explicit_prefill = False
+        self.explicit_prefill = True
 
     def cache_spec(self):
         return ("latent", self.R + self.rot)
@@ -220,26 +220,27 @@ class LatentAttention:
         q = seq_ops.linear(cq, self.w_uq, prec.empty(T, H * (dim + rot))).view(T, H, dim + rot)
         gate = proj[:, Q + R + rot:]
         att = prec.empty(T, H, vdim)
+        # rows of the lazily gathered scratch stay zero-padded to whole pages: every page a key tile touches exists
         explicit = (self.explicit_prefill and not prec.f32 and b.singles < b.E and (dim + rot, vdim) in seq_ops.MMA_HEAD_SIZES
-                    and R % 8 == 0 and (dim + rot) % 8 == 0)
-        if explicit:
-            self._explicit(q, gate, att, b, pages, prec)
+                    and R % 8 == 0 and (H * (dim + vdim)) % 8 == 0 and b.dense_pages is not None)
         if not explicit or b.singles:
+            # absorbed form; beside the explicit one it serves the single-token entries only (it still forms the absorbed query
+            # of every row: a mixed step is at most a few hundred rows)
             qlat = prec.empty(T, H, kd)
             seq_ops.linear_batched(q[:, :, :dim], self.w_ukT, qlat[:, :, :R])
             seq_ops.rotate_heads(q[:, :, dim:], qlat[:, :, R:], b.pos, self.freq_d, self.rot_dims)
             olat = prec.empty(T, H, R)
             seq_ops.attn_ragged(qlat.view(T, H * kd), pages, pages, gate, olat.view(T, H * R), b, H, 1, kd, R, self.scale, 0.0, PAGE,
                                 krow=kd, vrow=kd, gate_per_head=True, only_singles=explicit)
-            if explicit:
-                # rows of single-token entries only: the explicit form has written the others
-                seq_ops.linear_batched_rows(olat, self.w_uv, att, b.single_rows)
-            else:
-                seq_ops.linear_batched(olat, self.w_uv, att)
+            seq_ops.linear_batched(olat, self.w_uv, att)
+        if explicit:
+            # explicit heads for the multi-token entries (their rows of `att` are written last)
+            kx, vx = seq_ops.latent_expand(pages, b, self.w_ukv, H, dim, rot, vdim, R, PAGE, prec)
+            qr = q[:, :, dim:]
+            seq_ops.rotate_heads(qr, qr, b.pos, self.freq_d, self.rot_dims)
+            seq_ops.attn_ragged(q.view(T, H * (dim + rot)), kx, vx, gate, att.view(T, H * vdim), seq_ops.dense_view(b), H, H, dim + rot, vdim,
+                                self.scale, 0.0, PAGE, gate_per_head=True, skip_singles=True)
         return seq_ops.linear(att.view(T, H * vdim), self.w_o, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
-
-    def _explicit(self, q, gate, att, b, pages, prec):
-        raise NotImplementedError
 
 
 class SquaredReluFeedForward:

@@ -5,7 +5,7 @@ the shape allows TMA, the plain-FMA kernel otherwise) or fp32 (plain-FMA GEMMs o
 Norm statistics, attention scores and probabilities, recurrent states and the residual stream are fp32 in both.
 """
 import dataclasses
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -41,6 +41,14 @@ class StepBatch:
     max_pages: int
     singles: int = 0          # entries with one new token (decode rows)
     max_single_ctx: int = 0   # the longest context among them
+    # dense scratch layout of the entries with several new tokens (mixers that rebuild per-head keys / values from a compact
+    # cache): entry e owns rows [dense_row0[e], + ctx + n) of a dense matrix, starting on a page boundary, so that
+    # dense_pages[e] = consecutive page numbers is a page table over the scratch and the paged attention kernels read it
+    dense_row0: Optional[torch.Tensor] = None   # int32 [E]
+    dense_pages: Optional[torch.Tensor] = None  # int32 [E, dense_max_pages]
+    dense_max_pages: int = 0
+    dense_rows: int = 0       # rows of the scratch matrix (a multiple of the page size)
+    dense_max_len: int = 0    # the longest ctx + n among those entries
 
 
 def make_step_batch(entries: Sequence[dict]) -> StepBatch:
@@ -51,11 +59,21 @@ def make_step_batch(entries: Sequence[dict]) -> StepBatch:
     if E == 0 or min(ns) <= 0:
         raise ValueError("a step needs at least one entry and every entry at least one token")
     max_pages = max(1, max(len(e["pages"]) for e in entries))
-    buf = np.zeros(3 * T + 4 * E + E * max_pages, dtype=np.int32)
+    lens = [e["ctx"] + k if k > 1 else 0 for e, k in zip(entries, ns)]
+    dpages = [(l + 63) // 64 for l in lens]
+    dmax = max(1, max(dpages))
+    buf = np.zeros(3 * T + 4 * E + E * max_pages + E + E * dmax, dtype=np.int32)
     tokens, pos, row_entry = buf[:T], buf[T:2 * T], buf[2 * T:3 * T]
     o = 3 * T
     row0, n, ctx, slot = buf[o:o + E], buf[o + E:o + 2 * E], buf[o + 2 * E:o + 3 * E], buf[o + 3 * E:o + 4 * E]
-    pt = buf[o + 4 * E:].reshape(E, max_pages)
+    pt = buf[o + 4 * E:o + 4 * E + E * max_pages].reshape(E, max_pages)
+    o2 = o + 4 * E + E * max_pages
+    drow0, dpt = buf[o2:o2 + E], buf[o2 + E:].reshape(E, dmax)
+    page0 = 0
+    for i in range(E):
+        drow0[i] = page0 * 64
+        dpt[i, :dpages[i]] = np.arange(page0, page0 + dpages[i])
+        page0 += dpages[i]
     r = 0
     for i, e in enumerate(entries):
         k = ns[i]
@@ -71,8 +89,10 @@ def make_step_batch(entries: Sequence[dict]) -> StepBatch:
     o = 3 * T
     return StepBatch(T=T, E=E, max_n=max(ns), tokens=dev[:T], pos=dev[T:2 * T], row_entry=dev[2 * T:3 * T], row0=dev[o:o + E],
                      n=dev[o + E:o + 2 * E], ctx=dev[o + 2 * E:o + 3 * E], slot=dev[o + 3 * E:o + 4 * E],
-                     page_table=dev[o + 4 * E:].view(E, max_pages), max_pages=max_pages, singles=sum(k == 1 for k in ns),
-                     max_single_ctx=max([e["ctx"] for e, k in zip(entries, ns) if k == 1], default=0))
+                     page_table=dev[o + 4 * E:o2].view(E, max_pages), max_pages=max_pages, singles=sum(k == 1 for k in ns),
+                     max_single_ctx=max([e["ctx"] for e, k in zip(entries, ns) if k == 1], default=0),
+                     dense_row0=dev[o2:o2 + E], dense_pages=dev[o2 + E:].view(E, dmax), dense_max_pages=dmax, dense_rows=page0 * 64,
+                     dense_max_len=max(lens))
 
 
 class StaticDecodeBatch:
@@ -200,17 +220,17 @@ MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64)
 
 
 def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True,
-                krow=0, vrow=0, gate_per_head=False, only_singles=False):
+                krow=0, vrow=0, gate_per_head=False, only_singles=False, skip_singles=False):
     """Entries with several new rows go to a tiled kernel -- on the tensor cores for bf16 activations and the usual head
     sizes (fp32 probabilities as three bf16 terms), plain fp32 FMAs otherwise -- and entries with ONE new row (decoded tokens)
     to the key-split kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation
     order.  krow / vrow: elements per cache row when it is not G * dim / G * vdim (a latent cache: one row is key and value);
-    gate_per_head: the gate holds one scalar per head instead of one per output element; only_singles: rows of entries with
-    several new tokens are left alone (another form computes them)."""
+    gate_per_head: the gate holds one scalar per head instead of one per output element; only_singles / skip_singles: rows of
+    entries with several new tokens / with one new token are left alone (another form computes them)."""
     L, f32 = _lib.lib(), int(q.dtype == torch.float32)
     ldg = 0 if gate is None else gate.stride(0)
     gph = int(bool(gate_per_head))
-    singles = b.singles if decode_kernel else 0
+    singles = b.singles if (decode_kernel or skip_singles) else 0
     dense_rows = krow in (0, G * dim) and vrow in (0, G * vdim)
     if only_singles:
         pass
@@ -224,7 +244,7 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
                                     b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
                                     float(scale), float(softcap or 0.0), int(singles > 0), f32, int(krow), int(vrow), gph, _lib.stream()),
                    "pg_attn_ragged")
-    if singles:
+    if singles and not skip_singles:
         tiles = b.max_single_ctx // 32 + 1
         # enough CTAs for two waves, but at least two 32-key tiles for every warp of a CTA
         nsplit = max(1, min(-(-2 * _lib.num_sms() // (G * singles)), tiles // 16, 32))
@@ -288,6 +308,27 @@ def rotate_heads(src, dst, pos, freq, rot_dims):
     assert dst.shape == src.shape and src.dtype == dst.dtype and src.stride(2) == 1 and dst.stride(2) == 1
     _lib.check(_lib.lib().pg_rotate_heads(src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(), dst.stride(0), dst.stride(1), pos.data_ptr(),
                                           freq.data_ptr(), T, H, n, rot_dims, int(src.dtype == torch.float32), _lib.stream()), "pg_rotate_heads")
+
+
+def latent_expand(pages, b: StepBatch, w_ukv, H, dim, rot, vdim, rank, page, prec):
+    """Per-head keys [plain | rotated] and values of every multi-token entry's context + new tokens, rebuilt from the cached
+    latent rows into dense scratch: k [dense_rows, H * (dim + rot)], v [dense_rows, H * vdim] (read through b.dense_pages)."""
+    L, f32 = _lib.lib(), int(pages.dtype == torch.float32)
+    lat = prec.empty(b.dense_rows, rank)
+    _lib.check(L.pg_latent_gather(pages.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.dense_row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(),
+                                  lat.data_ptr(), b.E, b.dense_max_len, rank, rank + rot, f32, _lib.stream()), "pg_latent_gather")
+    up = linear(lat, w_ukv, prec.empty(b.dense_rows, H * (dim + vdim)))
+    k = prec.empty(b.dense_rows, H * (dim + rot))
+    v = prec.empty(b.dense_rows, H * vdim)
+    _lib.check(L.pg_latent_pack_kv(up.data_ptr(), up.stride(0), pages.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.dense_row0.data_ptr(),
+                                   b.n.data_ptr(), b.ctx.data_ptr(), k.data_ptr(), v.data_ptr(), b.E, b.dense_max_len, H, dim, rot, vdim, rank, f32,
+                                   _lib.stream()), "pg_latent_pack_kv")
+    return k, v
+
+
+def dense_view(b: StepBatch) -> StepBatch:
+    """The same step with the dense scratch layout in place of the cache's page table."""
+    return dataclasses.replace(b, page_table=b.dense_pages, max_pages=b.dense_max_pages)
 
 
 # ---- routed feed-forward ---------------------------------------------------------------------------------------------
