@@ -351,6 +351,19 @@ int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, cons
                    int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,
                    long long vrow, int gate_per_head, void* stream);
 
+/* The merge launch of pg_attn_decode on its own: rows of single-token entries from `partial` (fp32 [entries, H, nsplit, vdim + 2]:
+ * running max in natural-log units, sum, unnormalised accumulator), times the gate, to out [rows, H * vdim]. */
+int pg_attn_decode_merge(const float* partial, const void* gate, long long ldg, void* out, const int* entry_row0, const int* entry_n,
+                         int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, void* stream);
+/* Single-token entries of a latent-attention layer (absorbed form) on the tensor cores, bf16: q [rows, H, dim] against the
+ * one-row-per-token cache `pages` [.., page, dim] whose first vdim columns are the values; all heads of a token share one key
+ * tile (mma.sync, fp32 probabilities as three bf16 terms, values read from the key tile with ldmatrix.trans).  gate: one scalar
+ * per head (gate[t * ldg + h]) or NULL.  nsplit > 1: partial triples in the layout above, to be finished by pg_attn_decode_merge.
+ * (dim, vdim) in {(96,64), (160,128), (192,128), (288,256)}; anything else returns PG_ERR_ARG and belongs to pg_attn_decode. */
+int pg_attn_latent_decode_mma(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial,
+                              const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages,
+                              int page, int entries, int nsplit, int H, int dim, int vdim, float scale, void* stream);
+
 /* Decayed linear attention on qkv[t] = [q heads | k heads | v heads | ...] (q, k: H x dim, v: H x vdim; silu applied here):
  * per head S <- decay[h] * S + k v^T, out[t, h * vdim + :] = S^T q (fp32).  state: fp32 [slots, H, dim, vdim]; entry e
  * continues state[entry_slot[e]] (from zero when entry_ctx[e] == 0) and leaves its new state there.

@@ -201,6 +201,174 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Decoded tokens of a latent-attention layer in the absorbed form, on the tensor cores.  The cache holds ONE row per token
+// ([latent | rotated part], DIM wide) that is the key of every head and, in its first VDIM columns, the value: all H query heads of
+// a token are the rows of one tile against the same keys, so the tile is read once for all heads.
+//
+// CTA = (key split, block of up to 64 heads, entry); warp = 16 heads.  Keys pass in tiles of 64 rows through shared memory,
+// row-major.  S = Q K^T as in the kernel above (the Q fragments are re-read from shared memory per k step: DIM is up to 288).
+// P V takes its B operand from the SAME tile with ldmatrix.trans (key-major rows -> the k-pairs an m16n8k16 B fragment wants),
+// so the values are neither stored nor fetched separately; probabilities stay fp32 and enter as three bf16 terms.
+// With several key splits the (max, sum, accumulator) triples go to `partial` in the layout of pg_attn_decode and its merge
+// kernel finishes the rows.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
+                                                                     const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
+                                                                     float* __restrict__ partial, const int* __restrict__ entry_row0,
+                                                                     const int* __restrict__ entry_n, const int* __restrict__ entry_ctx,
+                                                                     const int* __restrict__ page_table, int max_pages, int page, int H, float scale) {
+  constexpr int KS = DIM / 16, NV = VDIM / 8, LD = DIM + 8;
+  static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && VDIM <= DIM, "tile shapes");
+  const int e = blockIdx.z, h0 = blockIdx.y * 64, split = blockIdx.x, nsplit = gridDim.x;
+  if (entry_n[e] != 1) return;
+  const int ctx = entry_ctx[e];
+  const long long t = entry_row0[e];
+  const int nrows = (blockDim.x >> 5) * 16;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);  // [nrows][LD]
+  bf16* Ks = Qs + nrows * LD;                 // [64][LD]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+  for (int id = threadIdx.x; id < nrows * (DIM / 8); id += blockDim.x) {
+    const int r = id / (DIM / 8), cc = id % (DIM / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (h0 + r < H) v = *reinterpret_cast<const uint4*>(q + (t * H + h0 + r) * DIM + cc * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LD + cc * 8) = v;
+  }
+  const int rl = warp * 16 + gq, rh = rl + 8;
+  float oacc[NV][4];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+  float m_l = -INFINITY, m_h = -INFINITY, l_l = 0.f, l_h = 0.f;
+  const int* pt = page_table + (long long)e * max_pages;
+  const int ntiles = ctx / 64 + 1;  // keys 0 .. ctx
+  const float sc2 = scale * 1.4426950408889634f;
+  // lane's row address inside a 16-key x 16-column block for ldmatrix.x4.trans: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15)
+  const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
+  for (int it = split; it < ntiles; it += nsplit) {
+    const int k0 = it * 64;
+    __syncthreads();
+    for (int id = threadIdx.x; id < 64 * (DIM / 8); id += blockDim.x) {
+      const int r = id / (DIM / 8), cc = id % (DIM / 8), j = k0 + r;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= ctx) v = *reinterpret_cast<const uint4*>(pages + ((long long)pt[j / page] * page + j % page) * DIM + cc * 8);
+      *reinterpret_cast<uint4*>(Ks + r * LD + cc * 8) = v;
+    }
+    __syncthreads();
+    float sacc[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+#pragma unroll 2
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(Qs + rl * LD + ks * 16 + 2 * tq);
+      a[1] = *reinterpret_cast<const uint32_t*>(Qs + rh * LD + ks * 16 + 2 * tq);
+      a[2] = *reinterpret_cast<const uint32_t*>(Qs + rl * LD + ks * 16 + 8 + 2 * tq);
+      a[3] = *reinterpret_cast<const uint32_t*>(Qs + rh * LD + ks * 16 + 8 + 2 * tq);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Ks + (nb * 8 + gq) * LD + ks * 16 + 2 * tq);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Ks + (nb * 8 + gq) * LD + ks * 16 + 8 + 2 * tq);
+        mma16816(sacc[nb], a, b0, b1);
+      }
+    }
+    float mx_l = -INFINITY, mx_h = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = k0 + nb * 8 + 2 * tq + (c & 1);
+        const float sc = key <= ctx ? sacc[nb][c] * sc2 : -INFINITY;
+        sacc[nb][c] = sc;
+        if (c & 2) mx_h = fmaxf(mx_h, sc); else mx_l = fmaxf(mx_l, sc);
+      }
+    mx_l = fmaxf(mx_l, __shfl_xor_sync(0xffffffffu, mx_l, 1)); mx_l = fmaxf(mx_l, __shfl_xor_sync(0xffffffffu, mx_l, 2));
+    mx_h = fmaxf(mx_h, __shfl_xor_sync(0xffffffffu, mx_h, 1)); mx_h = fmaxf(mx_h, __shfl_xor_sync(0xffffffffu, mx_h, 2));
+    const float mn_l = fmaxf(m_l, mx_l), mn_h = fmaxf(m_h, mx_h);  // finite: key k0 <= ctx is visible to every row
+    const float corr_l = exp2f(m_l - mn_l), corr_h = exp2f(m_h - mn_h);
+    float sum_l = 0.f, sum_h = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float p = exp2f(sacc[nb][c] - ((c & 2) ? mn_h : mn_l));
+        sacc[nb][c] = p;
+        if (c & 2) sum_h += p; else sum_l += p;
+      }
+    l_l = l_l * corr_l + sum_l;
+    l_h = l_h * corr_h + sum_h;
+    m_l = mn_l;
+    m_h = mn_h;
+#pragma unroll
+    for (int nv = 0; nv < NV; ++nv) {
+      oacc[nv][0] *= corr_l; oacc[nv][1] *= corr_l; oacc[nv][2] *= corr_h; oacc[nv][3] *= corr_h;
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t a1[4], a2[4], a3[4];
+      split3(sacc[2 * kk][0], sacc[2 * kk][1], a1[0], a2[0], a3[0]);
+      split3(sacc[2 * kk][2], sacc[2 * kk][3], a1[1], a2[1], a3[1]);
+      split3(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], a1[2], a2[2], a3[2]);
+      split3(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], a1[3], a2[3], a3[3]);
+      const bf16* vbase = Ks + (kk * 16 + lm_key) * LD + lm_col;
+#pragma unroll
+      for (int np = 0; np < NV / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vbase + np * 16);
+        mma16816(oacc[2 * np], a1, b0, b1);
+        mma16816(oacc[2 * np], a2, b0, b1);
+        mma16816(oacc[2 * np], a3, b0, b1);
+        mma16816(oacc[2 * np + 1], a1, b2, b3);
+        mma16816(oacc[2 * np + 1], a2, b2, b3);
+        mma16816(oacc[2 * np + 1], a3, b2, b3);
+      }
+    }
+  }
+  l_l += __shfl_xor_sync(0xffffffffu, l_l, 1); l_l += __shfl_xor_sync(0xffffffffu, l_l, 2);
+  l_h += __shfl_xor_sync(0xffffffffu, l_h, 1); l_h += __shfl_xor_sync(0xffffffffu, l_h, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int head = h0 + (half ? rh : rl);
+    if (head >= H) continue;
+    const float lsum = half ? l_h : l_l, mrow = half ? m_h : m_l;
+    if (nsplit == 1) {
+      float g = 1.0f / lsum;
+      if (gate != nullptr) g *= 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ldg + head])));
+#pragma unroll
+      for (int nv = 0; nv < NV; ++nv)
+        *reinterpret_cast<__nv_bfloat162*>(out + (t * H + head) * VDIM + nv * 8 + 2 * tq) =
+            __floats2bfloat162_rn(oacc[nv][2 * half] * g, oacc[nv][2 * half + 1] * g);
+    } else {
+      float* pp = partial + (((long long)e * H + head) * nsplit + split) * (VDIM + 2);
+      if (tq == 0) { pp[0] = mrow * 0.6931471805599453f; pp[1] = lsum; }  // the merge kernel works with natural exponentials
+#pragma unroll
+      for (int nv = 0; nv < NV; ++nv) {
+        pp[2 + nv * 8 + 2 * tq] = oacc[nv][2 * half];
+        pp[2 + nv * 8 + 2 * tq + 1] = oacc[nv][2 * half + 1];
+      }
+    }
+  }
+}
+
+template <int DIM, int VDIM>
+int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
+                  const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, cudaStream_t st) {
+  const int warps = H >= 64 ? 4 : (H + 15) / 16;
+  const size_t smem = ((size_t)(16 * warps + 64) * (DIM + 8)) * sizeof(bf16);
+  auto kern = attn_latent_decode_mma_kernel<DIM, VDIM>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+  kern<<<dim3(nsplit, (H + 63) / 64, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),
+                                                                      ldg, static_cast<bf16*>(out), partial, row0, n, ctx, pt, max_pages, page, H, scale);
+  pg_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+}
+
 template <int DIM, int VDIM>
 int launch(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0, const int* n, const int* ctx,
            const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, int gate_per_head, cudaStream_t st) {
@@ -239,4 +407,21 @@ extern "C" int pg_attn_ragged_mma(const void* q, const void* k_pages, const void
   PG_MMA(128, 64);
 #undef PG_MMA
   return PG_ERR_ARG;  // other head sizes: pg_attn_ragged
+}
+
+extern "C" int pg_attn_latent_decode_mma(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial,
+                                         const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages,
+                                         int page, int entries, int nsplit, int H, int dim, int vdim, float scale, void* stream) {
+  if (entries <= 0 || entries > 65535 || nsplit <= 0 || nsplit > 64 || H <= 0 || page <= 0 || (nsplit > 1 && partial == nullptr)) return PG_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return PG_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define PG_LAT(D, V) \
+  if (dim == D && vdim == V) \
+    return launch_latent<D, V>(q, pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, nsplit, H, scale, st)
+  PG_LAT(96, 64);
+  PG_LAT(160, 128);
+  PG_LAT(192, 128);
+  PG_LAT(288, 256);
+#undef PG_LAT
+  return PG_ERR_ARG;  // other row sizes: pg_attn_decode
 }

@@ -875,6 +875,19 @@ static int launch_attn_decode(const void* q, const void* kp, const void* vp, con
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
 
+extern "C" int pg_attn_decode_merge(const float* partial, const void* gate, long long ldg, void* out, const int* entry_row0, const int* entry_n,
+                                    int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, void* stream) {
+  if (entries <= 0 || entries > 65535 || nsplit <= 0 || H <= 0 || vdim <= 0 || partial == nullptr) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (act_f32)
+    attn_decode_merge_kernel<float><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const float*>(gate), ldg, static_cast<float*>(out), entry_row0, entry_n,
+                                                                     H, vdim, nsplit, gate_per_head);
+  else
+    attn_decode_merge_kernel<bf16><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), entry_row0, entry_n, H,
+                                                                    vdim, nsplit, gate_per_head);
+  PG_RET();
+}
+
 extern "C" int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                               int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,

@@ -219,6 +219,10 @@ def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_page
 MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64), (192, 128)}
 
 
+# (row width, value width) of a one-row-per-token cache the tensor-core decode kernel is instantiated for
+LATENT_MMA_SIZES = {(96, 64), (160, 128), (192, 128), (288, 256)}
+
+
 def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True,
                 krow=0, vrow=0, gate_per_head=False, only_singles=False, skip_singles=False):
     """Entries with several new rows go to a tiled kernel -- on the tensor cores for bf16 activations and the usual head
@@ -244,7 +248,20 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
                                     b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
                                     float(scale), float(softcap or 0.0), int(singles > 0), f32, int(krow), int(vrow), gph, _lib.stream()),
                    "pg_attn_ragged")
-    if singles and not skip_singles:
+    latent = (k_pages.data_ptr() == v_pages.data_ptr() and G == 1 and krow == vrow == dim and k_pages.shape[-1] == dim)
+    if (singles and not skip_singles and latent and tensor_cores and not f32 and (dim, vdim) in LATENT_MMA_SIZES and softcap in (0, 0.0, None)
+            and (gate is None or gph)):
+        # one-row-per-token cache, every head of a token against the same key tile: tensor cores
+        tiles = b.max_single_ctx // 64 + 1
+        nsplit = max(1, min(tiles, (4 * _lib.num_sms()) // (singles * -(-H // 64)), 32))
+        partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
+        _lib.check(L.pg_attn_latent_decode_mma(q.data_ptr(), k_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial), b.row0.data_ptr(),
+                                               b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit, H, dim, vdim,
+                                               float(scale), _lib.stream()), "pg_attn_latent_decode_mma")
+        if nsplit > 1:
+            _lib.check(L.pg_attn_decode_merge(partial.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.E, nsplit, H,
+                                              vdim, gph, 0, _lib.stream()), "pg_attn_decode_merge")
+    elif singles and not skip_singles:
         tiles = b.max_single_ctx // 32 + 1
         # enough CTAs for two waves, but at least two 32-key tiles for every warp of a CTA
         nsplit = max(1, min(-(-2 * _lib.num_sms() // (G * singles)), tiles // 16, 32))

@@ -203,6 +203,51 @@ def test_far_latent_row_at_page_borders_is_found(ctx, n, needle):
     assert w[needle] > 0.99
 
 
+@pytest.mark.parametrize("R,rot", [(64, 32), (128, 32), (128, 64), (256, 32)])
+@pytest.mark.parametrize("H,ctxs", [(3, [0, 63]), (16, [64, 700]), (40, [2100, 5]), (70, [129, 1023, 64])])
+def test_tensor_core_latent_decode_keeps_fp32_probabilities(R, rot, H, ctxs):
+    """Single-token entries in bf16 over the one-row cache: every head of a token against the same key tile, the values read
+    from the key tile itself, long contexts split over CTAs.  One row per entry stands out (its weight must survive the three
+    bf16 terms of the probabilities); compared with a float64 softmax over the same bf16 inputs."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    from paligemma_multimodal_system_b200.cache import SequenceStore
+    kd = R + rot
+    assert (kd, R) in seq_ops.LATENT_MMA_SIZES
+    g = torch.Generator().manual_seed(R + H)
+    store = SequenceStore([("latent", kd)], max_tokens=sum((c + 64) // 64 * 64 for c in ctxs) + 64, num_slots=len(ctxs), dtype=torch.bfloat16)
+    store.k_pages[0].fill_(1e4)
+    store.pool.take(1)
+    es, rows_all, qs = [], [], []
+    for i, ctx in enumerate(ctxs):
+        store.admit(i)
+        rec = store.reserve(i, ctx + 1)
+        rows = (torch.randn(ctx + 1, kd, generator=g) * 0.3).to(torch.bfloat16)
+        q = (torch.randn(H, kd, generator=g) * 0.3).to(torch.bfloat16)
+        needle = (ctx * 2) // 3
+        rows[needle] = (q[H // 2].float() * 3 / q[H // 2].float().norm()).to(torch.bfloat16)
+        q[H // 2] = (q[H // 2].float() * 6 / q[H // 2].float().norm()).to(torch.bfloat16)
+        for j in range(ctx + 1):
+            store.k_pages[0][rec.pages[j // 64], j % 64] = rows[j].cuda()
+        es.append(dict(tokens=[0], ctx=ctx, slot=rec.slot, pages=rec.pages))
+        rows_all.append(rows)
+        qs.append(q)
+    b = seq_ops.make_step_batch(es)
+    E = len(ctxs)
+    gate = torch.randn(E, H, generator=g).to(torch.bfloat16)
+    out = torch.empty(E, H * R, device="cuda", dtype=torch.bfloat16)
+    qd = torch.stack(qs).reshape(E, H * kd).cuda().contiguous()
+    seq_ops.attn_ragged(qd, store.k_pages[0], store.k_pages[0], gate.cuda(), out, b, H, 1, kd, R, 0.7, 0.0, 64, krow=kd, vrow=kd, gate_per_head=True)
+    plain = torch.empty_like(out)
+    seq_ops.attn_ragged(qd, store.k_pages[0], store.k_pages[0], gate.cuda(), plain, b, H, 1, kd, R, 0.7, 0.0, 64, krow=kd, vrow=kd, gate_per_head=True,
+                        tensor_cores=False)
+    for i in range(E):
+        s = (qs[i].double() @ rows_all[i].double().T) * 0.7
+        ref = (torch.softmax(s, -1) @ rows_all[i][:, :R].double()) * torch.sigmoid(gate[i].double())[:, None]
+        got = out[i].view(H, R).double().cpu()
+        assert float((got - ref).abs().max()) < 6e-3 * max(1.0, float(ref.abs().max())), (i, ctxs[i])
+        assert float((plain[i].view(H, R).double().cpu() - ref).abs().max()) < 6e-3 * max(1.0, float(ref.abs().max()))
+
+
 @pytest.mark.parametrize("kw", [dict(n_all=8, n_real=6, top=3, count=4, keep=2), dict(n_all=20, n_real=17, top=4, count=5, keep=2),
                                 dict(n_all=5, n_real=5, top=2, count=1, keep=1), dict(n_all=64, n_real=60, top=8, count=8, keep=3),
                                 dict(n_all=7, n_real=4, top=7, count=1, keep=1), dict(n_all=12, n_real=12, top=1, count=6, keep=1)])
