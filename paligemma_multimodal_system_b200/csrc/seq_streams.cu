@@ -39,52 +39,94 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const TI* _
   }
 }
 
-// One CTA per token row.  Column d of all S streams lives in one thread: the write-back is column-wise, so it is done in
-// place.  u goes to shared memory for the second pass after the block-wide mean square.
-template <typename TO>
+// One CTA per token row.  A thread holds V consecutive columns of all S streams (V = 4: 16-byte accesses): the write-back is
+// column-wise, so it is done in place.  u goes to shared memory for the second pass after the block-wide mean square.
+// SMAX = 4 or 8 bounds the unrolled stream loops.
+template <int V>
+struct VecF;
+template <>
+struct VecF<1> {
+  float v[1];
+  __device__ __forceinline__ void load(const float* p) { v[0] = *p; }
+  __device__ __forceinline__ void store(float* p) const { *p = v[0]; }
+};
+template <>
+struct VecF<4> {
+  float v[4];
+  __device__ __forceinline__ void load(const float* p) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+__device__ __forceinline__ void st_vec(float* p, const float* v, int n) {
+  if (n == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else p[0] = v[0];
+}
+__device__ __forceinline__ void st_vec(bf16* p, const float* v, int n) {
+  if (n == 4) {
+    uint2 u;
+    u.x = pg::pack_bf16(v[0], v[1]);
+    u.y = pg::pack_bf16(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else {
+    p[0] = __float2bfloat16_rn(v[0]);
+  }
+}
+
+template <typename TO, int V, int SMAX>
 __global__ void __launch_bounds__(256) stream_mix_norm_kernel(float* __restrict__ xs, const float* __restrict__ y, long long ldy,
                                                               const float* __restrict__ mix, const float* __restrict__ wr,
                                                               const float* __restrict__ rd, const float* __restrict__ norm_w,
                                                               TO* __restrict__ out_act, int S, int D, float eps) {
-  extern __shared__ float sm[];  // u[D], then 32 partial sums
+  extern __shared__ __align__(16) float sm[];  // u[D], then 32 partial sums
   float* us = sm;
   float* red = sm + D;
   __shared__ float Ms[MAX_STREAMS * MAX_STREAMS], bs[MAX_STREAMS], as[MAX_STREAMS];
   const long long t = blockIdx.x;
-  if (threadIdx.x < S * S && mix != nullptr) Ms[threadIdx.x] = mix[threadIdx.x];
-  if (threadIdx.x < S) {
-    bs[threadIdx.x] = wr != nullptr ? wr[threadIdx.x] : 0.f;
-    as[threadIdx.x] = rd != nullptr ? rd[threadIdx.x] : 0.f;
+  if (threadIdx.x < MAX_STREAMS * MAX_STREAMS) {
+    const int from = threadIdx.x / MAX_STREAMS, to = threadIdx.x % MAX_STREAMS;
+    Ms[threadIdx.x] = (mix != nullptr && from < S && to < S) ? mix[from * S + to] : 0.f;
+  }
+  if (threadIdx.x < MAX_STREAMS) {
+    bs[threadIdx.x] = (wr != nullptr && threadIdx.x < S) ? wr[threadIdx.x] : 0.f;
+    as[threadIdx.x] = (rd != nullptr && threadIdx.x < S) ? rd[threadIdx.x] : 0.f;
   }
   __syncthreads();
   float* xr = xs + t * S * D;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += 256) {
-    float x[MAX_STREAMS];
+  for (int d = threadIdx.x * V; d < D; d += 256 * V) {
+    VecF<V> x[SMAX];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) x[s] = s < S ? xr[(long long)s * D + d] : 0.f;
-    if (y != nullptr) {
-      const float yv = y[t * ldy + d];
-      float nx[MAX_STREAMS];
+    for (int s = 0; s < SMAX; ++s) {
+      if (s < S) x[s].load(xr + (long long)s * D + d);
+      else {
 #pragma unroll
-      for (int to = 0; to < MAX_STREAMS; ++to) {
-        float acc = 0.f;
-#pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
-          if (s < S && to < S) acc = fmaf(Ms[s * S + to], x[s], acc);
-        nx[to] = fmaf(bs[to < S ? to : 0], yv, acc);
+        for (int j = 0; j < V; ++j) x[s].v[j] = 0.f;
       }
+    }
+    if (y != nullptr) {
+      VecF<V> yv, nx[SMAX];
+      yv.load(y + t * ldy + d);
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s)
-        if (s < S) { x[s] = nx[s]; xr[(long long)s * D + d] = nx[s]; }
+      for (int to = 0; to < SMAX; ++to)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < SMAX; ++s) acc = fmaf(Ms[s * MAX_STREAMS + to], x[s].v[j], acc);  // rows / columns past S are zero
+          nx[to].v[j] = fmaf(bs[to], yv.v[j], acc);
+        }
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s)
+        if (s < S) { x[s] = nx[s]; nx[s].store(xr + (long long)s * D + d); }
     }
     if (rd != nullptr) {
-      float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s)
-        if (s < S) u = fmaf(as[s], x[s], u);
-      us[d] = u;
-      ss = fmaf(u, u, ss);
+      for (int j = 0; j < V; ++j) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s) u = fmaf(as[s], x[s].v[j], u);
+        us[d + j] = u;
+        ss = fmaf(u, u, ss);
+      }
     }
   }
   if (rd == nullptr) return;
@@ -96,11 +138,22 @@ __global__ void __launch_bounds__(256) stream_mix_norm_kernel(float* __restrict_
 #pragma unroll
   for (int w = 0; w < 8; ++w) tot += red[w];
   const float inv = 1.0f / sqrtf(tot / (float)D + eps);
-  for (int d = threadIdx.x; d < D; d += 256) {
-    float v = us[d] * inv;
-    if (norm_w != nullptr) v *= norm_w[d];
-    st_t(out_act, t * D + d, v);
+  for (int d = threadIdx.x * V; d < D; d += 256 * V) {
+    float v[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) v[j] = us[d + j] * inv * (norm_w != nullptr ? norm_w[d + j] : 1.0f);
+    st_vec(out_act + t * D + d, v, V);
   }
+}
+
+template <typename TO, int V, int SMAX>
+int launch_stream(float* xs, const float* y, long long ldy, const float* mix, const float* wr, const float* rd, const float* norm_w, void* out_act,
+                  int rows, int S, int D, float eps, size_t smem, cudaStream_t st) {
+  auto kern = stream_mix_norm_kernel<TO, V, SMAX>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+  kern<<<rows, 256, smem, st>>>(xs, y, ldy, mix, wr, rd, norm_w, static_cast<TO*>(out_act), S, D, eps);
+  pg_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
 
 }  // namespace
@@ -124,15 +177,19 @@ extern "C" int pg_stream_mix_norm(float* xs, const float* y, long long ldy, cons
   const size_t smem = ((size_t)D + 32) * sizeof(float);
   if (smem > 200 * 1024) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
+  // 16-byte accesses: rows of the streams, of y and of the output start on 16-byte boundaries (8 for a bf16 output)
+  const bool vec = D % 4 == 0 && ldy % 4 == 0 && ((reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out_act) & (out_f32 ? 15 : 7)) == 0;
+#define PG_STREAM(TO, V, SM) return launch_stream<TO, V, SM>(xs, y, ldy, mix, write_coef, read_coef, norm_w, out_act, rows, S, D, eps, smem, st)
   if (out_f32) {
-    auto kern = stream_mix_norm_kernel<float>;
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
-    kern<<<rows, 256, smem, st>>>(xs, y, ldy, mix, write_coef, read_coef, norm_w, static_cast<float*>(out_act), S, D, eps);
-  } else {
-    auto kern = stream_mix_norm_kernel<bf16>;
-    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
-    kern<<<rows, 256, smem, st>>>(xs, y, ldy, mix, write_coef, read_coef, norm_w, static_cast<bf16*>(out_act), S, D, eps);
+    if (vec && S <= 4) PG_STREAM(float, 4, 4);
+    if (vec) PG_STREAM(float, 4, 8);
+    if (S <= 4) PG_STREAM(float, 1, 4);
+    PG_STREAM(float, 1, 8);
   }
-  pg_count_launch(1);
-  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+  if (vec && S <= 4) PG_STREAM(bf16, 4, 4);
+  if (vec) PG_STREAM(bf16, 4, 8);
+  if (S <= 4) PG_STREAM(bf16, 1, 4);
+  PG_STREAM(bf16, 1, 8);
+#undef PG_STREAM
 }

@@ -284,7 +284,10 @@ class RoutedFeedForward:
 
     def pack(self, prec):
         w = self.w
-        self.w_router = w["router"].to("cuda", prec.dtype).contiguous()
+        # router rows padded with zeros to a multiple of 8: a shape the tensor-core product takes (the choice only reads n_all columns)
+        n_pad = (self.n_all + 7) // 8 * 8
+        self.w_router = torch.zeros(n_pad, self.D, device="cuda", dtype=prec.dtype)
+        self.w_router[:self.n_all] = w["router"].to("cuda", prec.dtype)
         self.correction = w["correction"].to("cuda", torch.float32).contiguous()
         if self.n_real:
             self.w_up = torch.stack(w["up"]).to("cuda", prec.dtype).contiguous()
@@ -294,8 +297,8 @@ class RoutedFeedForward:
 
     def __call__(self, h, b, prec):
         T = h.shape[0]
-        z = seq_ops.linear(h, self.w_router, torch.empty(T, self.n_all, device="cuda", dtype=torch.float32))
-        ids, wts, counts = seq_ops.moe_route(z, self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
+        z = seq_ops.linear(h, self.w_router, torch.empty(T, self.w_router.shape[0], device="cuda", dtype=torch.float32))
+        ids, wts, counts = seq_ops.moe_route(z[:, :self.n_all], self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
         plan = seq_ops.MoePlan(ids, counts, max(1, self.n_real))
         eo = None
         if self.n_real:
