@@ -206,8 +206,8 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 // ([latent | rotated part], DIM wide) that is the key of every head and, in its first VDIM columns, the value: all H query heads of
 // a token are the rows of one tile against the same keys, so the tile is read once for all heads.
 //
-// CTA = (key split, block of up to 64 heads, entry); warp = 16 heads.  Keys pass in tiles of 64 rows through shared memory,
-// row-major.  S = Q K^T as in the kernel above (the Q fragments are re-read from shared memory per k step: DIM is up to 288).
+// CTA = (key split, block of up to 64 heads, entry); warp = 16 heads.  Keys pass in tiles of 64 rows through two shared-memory
+// buffers, row-major, the next tile in flight (cp.async) while the current one is multiplied.  S = Q K^T as in the kernel above (the Q fragments are re-read from shared memory per k step: DIM is up to 288).
 // P V takes its B operand from the SAME tile with ldmatrix.trans (key-major rows -> the k-pairs an m16n8k16 B fragment wants),
 // so the values are neither stored nor fetched separately; probabilities stay fp32 and enter as three bf16 terms.
 // With several key splits the (max, sum, accumulator) triples go to `partial` in the layout of pg_attn_decode and its merge
@@ -216,6 +216,11 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
   const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+
+__device__ __forceinline__ void cp_async16(bf16* smem_dst, const bf16* gmem_src) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem_src) : "memory");
 }
 
 template <int DIM, int VDIM>
@@ -233,7 +238,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   const int nrows = (blockDim.x >> 5) * 16;
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);  // [nrows][LD]
-  bf16* Ks = Qs + nrows * LD;                 // [64][LD]
+  bf16* Kbuf = Qs + nrows * LD;               // two key tiles [64][LD]: the next one is fetched (cp.async) while this one is used
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   for (int id = threadIdx.x; id < nrows * (DIM / 8); id += blockDim.x) {
     const int r = id / (DIM / 8), cc = id % (DIM / 8);
@@ -251,15 +256,24 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   const float sc2 = scale * 1.4426950408889634f;
   // lane's row address inside a 16-key x 16-column block for ldmatrix.x4.trans: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15)
   const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
-  for (int it = split; it < ntiles; it += nsplit) {
+  auto fetch_tile = [&](int it, bf16* dst) {
     const int k0 = it * 64;
-    __syncthreads();
     for (int id = threadIdx.x; id < 64 * (DIM / 8); id += blockDim.x) {
       const int r = id / (DIM / 8), cc = id % (DIM / 8), j = k0 + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= ctx) v = *reinterpret_cast<const uint4*>(pages + ((long long)pt[j / page] * page + j % page) * DIM + cc * 8);
-      *reinterpret_cast<uint4*>(Ks + r * LD + cc * 8) = v;
+      bf16* d = dst + r * LD + cc * 8;
+      if (j <= ctx) cp_async16(d, pages + ((long long)pt[j / page] * page + j % page) * DIM + cc * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
+  };
+  int cur = 0;
+  if (split < ntiles) fetch_tile(split, Kbuf);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int it = split; it < ntiles; it += nsplit) {
+    const int k0 = it * 64;
+    const bf16* Ks = Kbuf + cur * 64 * LD;
+    if (it + nsplit < ntiles) fetch_tile(it + nsplit, Kbuf + (cur ^ 1) * 64 * LD);  // that buffer was released by the barrier below
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group has landed: this tile
     __syncthreads();
     float sacc[8][4];
 #pragma unroll
@@ -329,6 +343,8 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
         mma16816(oacc[2 * np + 1], a3, b2, b3);
       }
     }
+    __syncthreads();  // every warp is done with this buffer before the next iteration refills it
+    cur ^= 1;
   }
   l_l += __shfl_xor_sync(0xffffffffu, l_l, 1); l_l += __shfl_xor_sync(0xffffffffu, l_l, 2);
   l_h += __shfl_xor_sync(0xffffffffu, l_h, 1); l_h += __shfl_xor_sync(0xffffffffu, l_h, 2);
@@ -360,7 +376,7 @@ template <int DIM, int VDIM>
 int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
                   const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, cudaStream_t st) {
   const int warps = H >= 64 ? 4 : (H + 15) / 16;
-  const size_t smem = ((size_t)(16 * warps + 64) * (DIM + 8)) * sizeof(bf16);
+  const size_t smem = ((size_t)(16 * warps + 2 * 64) * (DIM + 8)) * sizeof(bf16);
   auto kern = attn_latent_decode_mma_kernel<DIM, VDIM>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   kern<<<dim3(nsplit, (H + 63) / 64, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),

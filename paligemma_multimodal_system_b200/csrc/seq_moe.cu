@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x,
 }
 
 // The same product for bf16 operands on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tile = 64 sorted rows of one
-// expert x 128 features, 4 warps of 32 x 64, k in steps of 32 through shared memory; the next step's operands are fetched into
+// expert x 128 (or 64) features, 4 warps of 32 x 64 (32), k in steps of 64 through shared memory; the next step's operands are fetched into
 // registers (16-byte loads; the x rows are gathered through the sorted order) while the current one is multiplied.
 __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -247,17 +247,20 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TO>
+template <typename TO, int BN>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
                                                            const bf16* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
                                                            long long ldo, const int* __restrict__ plan, int F, int K, int act) {
-  constexpr int LD = 40;  // bf16 elements per shared row: 32 + 8 (conflict-free fragment reads)
+  constexpr int KT = 64;      // k step
+  constexpr int LD = KT + 8;  // bf16 elements per shared row (conflict-free fragment reads)
+  constexpr int NI = BN / 16; // 8-feature blocks per warp (two warps side by side)
+  constexpr int CA = MOE_TILE * (KT / 8) / 128, CB = BN * (KT / 8) / 128;  // 16-byte chunks per thread and k step
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
-  const int f0 = blockIdx.x * 128;
+  const int f0 = blockIdx.x * BN;
   __shared__ __align__(16) bf16 As[MOE_TILE * LD];
-  __shared__ __align__(16) bf16 Bs[128 * LD];
+  __shared__ __align__(16) bf16 Bs[BN * LD];
   __shared__ long long src[MOE_TILE];
   if (threadIdx.x < MOE_TILE) {
     long long s = -1;
@@ -268,44 +271,44 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
   const bf16* we = w + (long long)e * expert_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   const int wm = warp >> 1, wn = warp & 1;
-  // this thread's 16-byte chunks of a k step: A chunks id = tid, tid + 128 (row id / 4, columns 8 (id % 4)); B chunks id = tid + 128 j
-  uint4 ra[2], rb[4];
+  // chunk id -> row id / 8, columns 8 (id % 8)
+  uint4 ra[CA], rb[CB];
   auto fetch = [&](int k0) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int id = threadIdx.x + 128 * j, r = id >> 2, c = (id & 3) * 8;
+    for (int j = 0; j < CA; ++j) {
+      const int id = threadIdx.x + 128 * j, r = id >> 3, c = (id & 7) * 8;
       ra[j] = make_uint4(0, 0, 0, 0);
       if (src[r] >= 0 && k0 + c < K) ra[j] = *reinterpret_cast<const uint4*>(x + src[r] * ldx + k0 + c);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int id = threadIdx.x + 128 * j, r = id >> 2, c = (id & 3) * 8;
+    for (int j = 0; j < CB; ++j) {
+      const int id = threadIdx.x + 128 * j, r = id >> 3, c = (id & 7) * 8;
       rb[j] = make_uint4(0, 0, 0, 0);
       if (f0 + r < F && k0 + c < K) rb[j] = *reinterpret_cast<const uint4*>(we + (long long)(f0 + r) * ldw + k0 + c);
     }
   };
-  float acc[2][8][4];
+  float acc[2][NI][4];
 #pragma unroll
   for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-    for (int ni = 0; ni < 8; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+    for (int ni = 0; ni < NI; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
   fetch(0);
-  for (int k0 = 0; k0 < K; k0 += 32) {
+  for (int k0 = 0; k0 < K; k0 += KT) {
     __syncthreads();  // the previous step's fragments have been read
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < CA; ++j) {
       const int id = threadIdx.x + 128 * j;
-      *reinterpret_cast<uint4*>(As + (id >> 2) * LD + (id & 3) * 8) = ra[j];
+      *reinterpret_cast<uint4*>(As + (id >> 3) * LD + (id & 7) * 8) = ra[j];
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < CB; ++j) {
       const int id = threadIdx.x + 128 * j;
-      *reinterpret_cast<uint4*>(Bs + (id >> 2) * LD + (id & 3) * 8) = rb[j];
+      *reinterpret_cast<uint4*>(Bs + (id >> 3) * LD + (id & 7) * 8) = rb[j];
     }
     __syncthreads();
-    if (k0 + 32 < K) fetch(k0 + 32);
+    if (k0 + KT < K) fetch(k0 + KT);
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
+    for (int ks = 0; ks < KT / 16; ++ks) {
       uint32_t a[2][4];
 #pragma unroll
       for (int mi = 0; mi < 2; ++mi) {
@@ -316,8 +319,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
         a[mi][3] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD + 8);
       }
 #pragma unroll
-      for (int ni = 0; ni < 8; ++ni) {
-        const bf16* bp = Bs + (64 * wn + 8 * ni + gq) * LD + ks * 16 + 2 * tq;
+      for (int ni = 0; ni < NI; ++ni) {
+        const bf16* bp = Bs + ((BN / 2) * wn + 8 * ni + gq) * LD + ks * 16 + 2 * tq;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp), b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
         mma_bf16_16816(acc[0][ni], a[0], b0, b1);
         mma_bf16_16816(acc[1][ni], a[1], b0, b1);
@@ -327,10 +330,10 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
 #pragma unroll
   for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-    for (int ni = 0; ni < 8; ++ni)
+    for (int ni = 0; ni < NI; ++ni)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int r = 32 * wm + 16 * mi + gq + ((c & 2) ? 8 : 0), f = f0 + 64 * wn + 8 * ni + 2 * tq + (c & 1);
+        const int r = 32 * wm + 16 * mi + gq + ((c & 2) ? 8 : 0), f = f0 + (BN / 2) * wn + 8 * ni + 2 * tq + (c & 1);
         if (r < nr && f < F) {
           float v = acc[mi][ni][c];
           if (act == 2) { v = fmaxf(v, 0.f); v *= v; }
@@ -393,13 +396,16 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
   // bf16 operands whose rows can be fetched in 16-byte pieces go to the tensor cores
   if (!in_f32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
-    dim3 g2((F + 127) / 128, max_tiles);
-    if (out_f32)
-      moe_gemm_mma_kernel<float><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw,
-                                                    static_cast<float*>(out), ldo, plan, F, K, act);
-    else
-      moe_gemm_mma_kernel<bf16><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw,
-                                                   static_cast<bf16*>(out), ldo, plan, F, K, act);
+    // few tiles (decode: a handful of rows per expert, the weights stream once): narrower feature tiles for more CTAs in flight
+    const bool narrow = (long long)max_tiles * ((F + 127) / 128) < 2LL * pg::num_sms();
+    const int BN = narrow ? 64 : 128;
+    dim3 g2((F + BN - 1) / BN, max_tiles);
+#define PG_MOE_MMA(TO, BNV) \
+  moe_gemm_mma_kernel<TO, BNV><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw, \
+                                                   static_cast<TO*>(out), ldo, plan, F, K, act)
+    if (out_f32) { if (narrow) PG_MOE_MMA(float, 64); else PG_MOE_MMA(float, 128); }
+    else { if (narrow) PG_MOE_MMA(bf16, 64); else PG_MOE_MMA(bf16, 128); }
+#undef PG_MOE_MMA
     PG_RET();
   }
   if (in_f32 && out_f32)
