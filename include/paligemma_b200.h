@@ -418,7 +418,9 @@ int pg_latent_pack_kv(const void* up, long long ld_up, const void* pages, const 
  *   pair_row[pair] = its sorted row (-1: identity expert).  fill: int32 [n_real] scratch.
  * pg_moe_gemm: out[row, f] = act(sum_k x[src(row), k] * w[expert(row)][f, k]) for the rows of every tile; src(row) =
  *   sorted_pair[row] / src_div when src_div > 0, else row.  w: [n_real] matrices [F, K] (pitch ldw, expert_stride elements apart).
- *   act: 0 none, 2 relu(x)^2.
+ *   act: 0 none, 2 relu(x)^2.  x_expert_off / out_expert_off: elements added to x / out per expert index (0 for routed
+ *   experts).  With a host-made plan of (batch index, first row, rows) tiles over the SAME rows for every index this is a batched
+ *   product whose operands are column slices: out[:, b, :] = x[:, b, :] w[b]^T (per-head projections on the tensor cores).
  * pg_moe_combine: y[t, :] = sum_k weights[t, k] * (pair_row[t, k] < 0 ? h[t, :] : expert_out[pair_row[t, k], :]) + shared_out[t, :]
  *   (shared_out may be NULL). */
 int pg_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int* counts, int tokens, int n_all,
@@ -427,7 +429,8 @@ int pg_moe_tile_rows(void);
 int pg_moe_plan(const int* counts, const int* ids, int* offsets, int* fill, int* plan, int* sorted_pair, int* pair_row, int pairs,
                 int n_real, int max_tiles, void* stream);
 int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
-                void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, void* stream);
+                void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32,
+                long long x_expert_off, long long out_expert_off, void* stream);
 int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
                    long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream);
 

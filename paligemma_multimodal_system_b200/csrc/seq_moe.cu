@@ -186,11 +186,14 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
                                                        const TI* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
-                                                       long long ldo, const int* __restrict__ plan, int F, int K, int act) {
+                                                       long long ldo, const int* __restrict__ plan, int F, int K, int act, long long x_off,
+                                                       long long out_off) {
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
   const int f0 = blockIdx.x * 64;
+  x += e * x_off;      // batched use: every "expert" reads its own column slice of x and writes its own slice of out
+  out += e * out_off;
   __shared__ float xs[16][MOE_TILE + 4];
   __shared__ float ws[16][64 + 4];
   __shared__ long long src[MOE_TILE];
@@ -250,7 +253,8 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
 template <typename TO, int BN>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
                                                            const bf16* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
-                                                           long long ldo, const int* __restrict__ plan, int F, int K, int act) {
+                                                           long long ldo, const int* __restrict__ plan, int F, int K, int act, long long x_off,
+                                                           long long out_off) {
   constexpr int KT = 64;      // k step
   constexpr int LD = KT + 8;  // bf16 elements per shared row (conflict-free fragment reads)
   constexpr int NI = BN / 16; // 8-feature blocks per warp (two warps side by side)
@@ -259,6 +263,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
   if (tile >= plan[0]) return;
   const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
   const int f0 = blockIdx.x * BN;
+  x += e * x_off;
+  out += e * out_off;
   __shared__ __align__(16) bf16 As[MOE_TILE * LD];
   __shared__ __align__(16) bf16 Bs[BN * LD];
   __shared__ long long src[MOE_TILE];
@@ -389,12 +395,13 @@ extern "C" int pg_moe_plan(const int* counts, const int* ids, int* offsets, int*
 }
 
 extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
-                           void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, void* stream) {
+                           void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, long long x_expert_off,
+                           long long out_expert_off, void* stream) {
   if (max_tiles <= 0 || max_tiles > 65535 || F <= 0 || K <= 0 || src_div < 0) return PG_ERR_ARG;
   dim3 grid((F + 63) / 64, max_tiles);
   cudaStream_t st = PG_ST(stream);
   // bf16 operands whose rows can be fetched in 16-byte pieces go to the tensor cores
-  if (!in_f32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 &&
+  if (!in_f32 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && expert_stride % 8 == 0 && x_expert_off % 8 == 0 &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
     // few tiles (decode: a handful of rows per expert, the weights stream once): narrower feature tiles for more CTAs in flight
     const bool narrow = (long long)max_tiles * ((F + 127) / 128) < 2LL * pg::num_sms();
@@ -402,7 +409,7 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
     dim3 g2((F + BN - 1) / BN, max_tiles);
 #define PG_MOE_MMA(TO, BNV) \
   moe_gemm_mma_kernel<TO, BNV><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw, \
-                                                   static_cast<TO*>(out), ldo, plan, F, K, act)
+                                                   static_cast<TO*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off)
     if (out_f32) { if (narrow) PG_MOE_MMA(float, 64); else PG_MOE_MMA(float, 128); }
     else { if (narrow) PG_MOE_MMA(bf16, 64); else PG_MOE_MMA(bf16, 128); }
 #undef PG_MOE_MMA
@@ -410,13 +417,13 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
   }
   if (in_f32 && out_f32)
     moe_gemm_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, sorted_pair, src_div, static_cast<const float*>(w), expert_stride,
-                                                       ldw, static_cast<float*>(out), ldo, plan, F, K, act);
+                                                       ldw, static_cast<float*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off);
   else if (!in_f32 && out_f32)
     moe_gemm_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride,
-                                                      ldw, static_cast<float*>(out), ldo, plan, F, K, act);
+                                                      ldw, static_cast<float*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off);
   else if (!in_f32 && !out_f32)
     moe_gemm_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride,
-                                                     ldw, static_cast<bf16*>(out), ldo, plan, F, K, act);
+                                                     ldw, static_cast<bf16*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off);
   else
     return PG_ERR_ARG;
   PG_RET();

@@ -296,13 +296,42 @@ def stream_mix_norm(xs, y=None, mix=None, write=None, read=None, norm_w=None, ou
 
 
 # ---- latent attention ------------------------------------------------------------------------------------------------
+_BATCH_PLANS = {}
+
+
+def _batch_plan(T, B):
+    """Tile list (batch index, first row, rows) of a batched product over the same T rows for every index, in the layout of
+    pg_moe_plan; made once per (T, B) on the host."""
+    key = (T, B)
+    if key not in _BATCH_PLANS:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        tile = _lib.lib().pg_moe_tile_rows()
+        rows = [(b, r0, min(tile, T - r0)) for b in range(B) for r0 in range(0, T, tile)]
+        buf = np.zeros(4 + 3 * len(rows), dtype=np.int32)
+        buf[0] = len(rows)
+        buf[4:] = np.asarray(rows, dtype=np.int32).reshape(-1)
+        _BATCH_PLANS[key] = (torch.from_numpy(buf).to("cuda"), len(rows))
+        torch.cuda.current_stream().synchronize()
+    return _BATCH_PLANS[key]
+
+
 def linear_batched(x, w, out):
     """out[:, b, :] = x[:, b, :] @ w[b].T for every b: x [T, B, K] and out [T, B, F] are views with unit last stride, w [B, F, K].
-    Plain fp32 FMAs (bf16 or fp32 operands)."""
+    bf16 operands whose slices start on 16-byte boundaries run on the tensor cores (the grouped kernel of the routed experts with
+    one "expert" per batch index); everything else on plain fp32 FMAs."""
     T, B, K = x.shape
     F = w.shape[1]
     assert w.shape == (B, F, K) and out.shape == (T, B, F) and x.dtype == w.dtype and w.is_contiguous()
     assert x.stride(2) == 1 and out.stride(2) == 1
+    if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and len(_BATCH_PLANS) < 4096):
+        plan = _batch_plan(T, B)
+        if plan is not None and plan[1] <= 65535:
+            _lib.check(_lib.lib().pg_moe_gemm(x.data_ptr(), x.stride(0), plan[0].data_ptr(), 0, w.data_ptr(), F * K, K, out.data_ptr(), out.stride(0),
+                                              plan[0].data_ptr(), plan[1], F, K, 0, 0, int(out.dtype == torch.float32), x.stride(1), out.stride(1),
+                                              _lib.stream()), "pg_moe_gemm")
+            return out
     _lib.check(_lib.lib().pg_gemm_simt_batched(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), K, F * K, out.data_ptr(), out.stride(0),
                                                out.stride(1), T, F, K, B, int(x.dtype == torch.float32), int(out.dtype == torch.float32),
                                                _lib.stream()), "pg_gemm_simt_batched")
@@ -386,7 +415,7 @@ def moe_gemm(x, plan: MoePlan, w, out, gather, act=0):
     assert w.is_contiguous() and x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == K and out.shape[1] == F
     _lib.check(_lib.lib().pg_moe_gemm(x.data_ptr(), x.stride(0), plan.sorted_pair.data_ptr(), plan.top if gather else 0, w.data_ptr(), F * K, K,
                                       out.data_ptr(), out.stride(0), plan.plan.data_ptr(), plan.max_tiles, F, K, int(act),
-                                      int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_moe_gemm")
+                                      int(x.dtype == torch.float32), int(out.dtype == torch.float32), 0, 0, _lib.stream()), "pg_moe_gemm")
     return out
 
 

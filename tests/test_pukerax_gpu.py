@@ -203,6 +203,24 @@ def test_far_latent_row_at_page_borders_is_found(ctx, n, needle):
     assert w[needle] > 0.99
 
 
+@pytest.mark.parametrize("T,B,K,F,extra", [(1, 3, 64, 256, 32), (64, 32, 64, 256, 32), (130, 5, 256, 64, 0), (70, 2, 40, 24, 8), (9, 4, 20, 12, 6), (200, 3, 33, 17, 1)])
+@pytest.mark.parametrize("f32", [False, True])
+def test_per_head_products_on_column_slices(T, B, K, F, extra, f32):
+    """out[:, b, :] = x[:, b, :K] w[b]^T with x and out column slices of wider per-head rows (the absorbed query and the value up
+    projection); bf16 slices on 16-byte boundaries take the tensor-core kernel, the others plain FMAs."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    dt = torch.float32 if f32 else torch.bfloat16
+    g = torch.Generator().manual_seed(T + K)
+    xw = torch.randn(T, B, K + extra, generator=g).to(dt)
+    w = (torch.randn(B, F, K, generator=g) / K ** 0.5).to(dt)
+    outw = torch.full((T, B, F + extra), 7.0, dtype=dt).cuda()
+    xd = xw.cuda()
+    seq_ops.linear_batched(xd[:, :, :K], w.cuda().contiguous(), outw[:, :, :F])
+    ref = torch.einsum("tbk,bfk->tbf", xw[:, :, :K].double(), w.double())
+    assert rel_err(outw[:, :, :F].float(), ref) < (1e-5 if f32 else 6e-3)
+    assert bool((outw[:, :, F:] == 7.0).all())  # nothing written outside the slice
+
+
 @pytest.mark.parametrize("R,rot", [(64, 32), (128, 32), (128, 64), (256, 32)])
 @pytest.mark.parametrize("H,ctxs", [(3, [0, 63]), (16, [64, 700]), (40, [2100, 5]), (70, [129, 1023, 64])])
 def test_tensor_core_latent_decode_keeps_fp32_probabilities(R, rot, H, ctxs):
