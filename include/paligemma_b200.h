@@ -431,6 +431,10 @@ int pg_moe_plan(const int* counts, const int* ids, int* offsets, int* fill, int*
 int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
                 void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32,
                 long long x_expert_off, long long out_expert_off, void* stream);
+/* xg[row, 0:D] = x[sorted_pair[row] / top, 0:D] for row < *total_rows (device: offsets[n_real] of pg_moe_plan): the tokens of
+ * every expert as one contiguous run of rows, for per-expert dense products. */
+int pg_moe_gather_rows(const void* x, long long ldx, const int* sorted_pair, const int* total_rows, int top, void* xg, long long ldg,
+                       int max_rows, int D, int act_f32, void* stream);
 int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
                    long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream);
 

@@ -348,6 +348,18 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
       }
 }
 
+// xg[row, :] = x[sorted_pair[row] / top, :] for the `rows` sorted pairs that exist (rows read from offsets[n_real] on the device)
+template <typename TA>
+__global__ void moe_gather_rows_kernel(const TA* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, const int* __restrict__ total,
+                                       int top, TA* __restrict__ xg, long long ldg, int D) {
+  const int n = *total;
+  for (int row = blockIdx.x; row < n; row += gridDim.x) {
+    const TA* src = x + (long long)(sorted_pair[row] / top) * ldx;
+    TA* dst = xg + (long long)row * ldg;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+  }
+}
+
 template <typename TA>
 __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long long ldy, const int* __restrict__ pair_row, const int* __restrict__ ids,
                                    const float* __restrict__ weights, const TA* __restrict__ h, long long ldh, const float* __restrict__ shared_out,
@@ -426,6 +438,17 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
                                                      ldw, static_cast<bf16*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off);
   else
     return PG_ERR_ARG;
+  PG_RET();
+}
+
+extern "C" int pg_moe_gather_rows(const void* x, long long ldx, const int* sorted_pair, const int* total_rows, int top, void* xg, long long ldg,
+                                  int max_rows, int D, int act_f32, void* stream) {
+  if (max_rows <= 0 || D <= 0 || top <= 0) return PG_ERR_ARG;
+  const int grid = max_rows < 16384 ? max_rows : 16384;
+  if (act_f32)
+    moe_gather_rows_kernel<float><<<grid, 128, 0, PG_ST(stream)>>>(static_cast<const float*>(x), ldx, sorted_pair, total_rows, top, static_cast<float*>(xg), ldg, D);
+  else
+    moe_gather_rows_kernel<bf16><<<grid, 128, 0, PG_ST(stream)>>>(static_cast<const bf16*>(x), ldx, sorted_pair, total_rows, top, static_cast<bf16*>(xg), ldg, D);
   PG_RET();
 }
 

@@ -295,13 +295,33 @@ class RoutedFeedForward:
         if self.shared is not None:
             self.shared.pack(prec)
 
+    # at least this many (token, choice) pairs per real expert on average before a host round trip for the counts pays
+    DENSE_SEGMENT_ROWS = 256
+
+    def _dense_segments(self, T, prec):
+        return (not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
+                and not torch.cuda.is_current_stream_capturing())
+
     def __call__(self, h, b, prec):
         T = h.shape[0]
         z = seq_ops.linear(h, self.w_router, torch.empty(T, self.w_router.shape[0], device="cuda", dtype=torch.float32))
         ids, wts, counts = seq_ops.moe_route(z[:, :self.n_all], self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
         plan = seq_ops.MoePlan(ids, counts, max(1, self.n_real))
         eo = None
-        if self.n_real:
+        if self.n_real and self._dense_segments(T, prec):
+            # many rows per expert (prompt portions): the pair counts come to the host once per layer, every expert's tokens are
+            # gathered into one contiguous run and each expert is two dense tcgen05 products on its run
+            per = counts.tolist()
+            xg = seq_ops.moe_gather_rows(h, plan, prec.empty(plan.pairs, self.D))
+            mid = prec.empty(plan.pairs, self.F)
+            eo = torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32)
+            off = 0
+            for e, c in enumerate(per):
+                if c:
+                    seq_ops.linear(xg[off:off + c], self.w_up[e], mid[off:off + c], act=seq_ops.ACT_RELU2)
+                    seq_ops.linear(mid[off:off + c], self.w_down[e], eo[off:off + c])
+                    off += c
+        elif self.n_real:
             mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_RELU2)
             eo = seq_ops.moe_gemm(mid, plan, self.w_down, torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32), gather=False)
         sh = self.shared(h, b, prec) if self.shared is not None else None

@@ -419,6 +419,14 @@ def moe_gemm(x, plan: MoePlan, w, out, gather, act=0):
     return out
 
 
+def moe_gather_rows(x, plan: MoePlan, out):
+    """out[row] = x[token of sorted pair `row`]: every expert's tokens as one contiguous run of rows."""
+    assert x.dtype == out.dtype and x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] >= plan.pairs
+    _lib.check(_lib.lib().pg_moe_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pair.data_ptr(), plan.offsets[-1:].data_ptr(), plan.top, out.data_ptr(),
+                                             out.stride(0), plan.pairs, x.shape[1], int(x.dtype == torch.float32), _lib.stream()), "pg_moe_gather_rows")
+    return out
+
+
 def moe_combine(expert_out, plan: MoePlan, ids, weights, h, shared_out, y):
     T, D = y.shape
     assert y.dtype == torch.float32 and y.is_contiguous() and h.stride(1) == 1

@@ -314,6 +314,31 @@ def test_feed_forwards_alone(mlp, dtype, tol, T):
     assert rel_err(got, ref) < tol
 
 
+@pytest.mark.parametrize("T", [40, 300])
+def test_routed_experts_as_dense_runs_per_expert(T, monkeypatch):
+    """Prompt-sized steps gather every expert's tokens into one run of rows and use the dense products; forced here at a small
+    size, against the oracle and against the grouped kernel (same choice, bf16 rounding apart)."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    from paligemma_multimodal_system_b200.mixers import RoutedFeedForward
+    from paligemma_multimodal_system_b200.modeling_pukerax import _feed_forward
+    D, mlp = 64, moe(experts=6, identity=2, top=3, count=4, keep=2, ff=32, shared=16)
+    cfg = make_cfg([layer(mlp)], width=D)
+    w = {k[len("l0.mlp."):]: v for k, v in O.random_weights(cfg, seed=14).items() if k.startswith("l0.mlp.")}
+    g = torch.Generator().manual_seed(T)
+    h = torch.randn(T, D, generator=g).to(torch.bfloat16).float()
+    ref = O.feed_forward(h, {"f." + k: v for k, v in w.items()}, "f.", mlp)
+    ff = _feed_forward(D, mlp)
+    ff.load(lambda name, shape: w[name].to(torch.bfloat16), "")
+    prec = seq_ops.Precision(torch.bfloat16)
+    ff.pack(prec)
+    hd = h.to(torch.bfloat16).cuda().contiguous()
+    grouped = ff(hd, None, prec)
+    monkeypatch.setattr(RoutedFeedForward, "DENSE_SEGMENT_ROWS", 0)
+    assert ff._dense_segments(T, prec)
+    dense_runs = ff(hd, None, prec)
+    assert rel_err(dense_runs, ref) < 2e-2 and rel_err(dense_runs, grouped.cpu()) < 1e-2
+
+
 def test_causal_edge_row_just_outside_is_not_seen():
     """Position i must see row i and not row i + 1: the later rows of the portion carry huge values in the cache by the time
     the attention runs (the whole portion is written first)."""
