@@ -24,6 +24,18 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// four 8 x 8 bf16 matrices from shared memory, transposed: key-major value rows -> the k-pairs an m16n8k16 B fragment wants
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+
+// 16-byte asynchronous copy global -> shared (cp.async group semantics)
+__device__ __forceinline__ void cp_async16(bf16* smem_dst, const bf16* gmem_src) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem_src) : "memory");
+}
+
 // tanh to fp32 accuracy without the library's slow path: odd series below 0.1 (next term 17 x^7 / 315 < 6e-10), else
 // 1 - 2 / (exp(2|x|) + 1), whose absolute error of ~1e-7 is relative there as well
 __device__ __forceinline__ float tanh32(float x) {
@@ -52,7 +64,8 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
                                                               const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                               const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
                                                               int page, int H, int G, float scale, float softcap, int skip_single, int gate_per_head) {
-  constexpr int KS = DIM / 16, NV = VDIM / 8, QP = DIM + 8, VP = 64 + 8;
+  constexpr int KS = DIM / 16, NV = VDIM / 8, QP = DIM + 8, VLD = VDIM + 8;
+  static_assert(VDIM % 16 == 0, "value blocks are fetched in pairs");
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
   const int n = entry_n[e], ctx = entry_ctx[e], row0 = entry_row0[e];
   if (skip_single && n == 1) return;
@@ -61,8 +74,8 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
   if (r0 >= rows) return;
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);  // [64][QP]
-  bf16* Ks = Qs + 64 * QP;                    // [64][QP]
-  bf16* Vt = Ks + 64 * QP;                    // [VDIM][VP]  (transposed: value column x key)
+  bf16* Kb = Qs + 64 * QP;                    // two key tiles [64][QP]
+  bf16* Vb = Kb + 2 * 64 * QP;                // two value tiles [64][VLD], key-major (P V reads them through ldmatrix.trans)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   // Q tile (zero rows past the end)
   for (int id = threadIdx.x; id < 64 * (DIM / 8); id += 128) {
@@ -93,24 +106,36 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
   const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   const int* pt = page_table + (long long)e * max_pages;
   const long long krow = (long long)G * DIM, vrow = (long long)G * VDIM;
-  for (int k0 = 0; k0 <= kmax; k0 += 64) {
-    __syncthreads();
+  // K / V tiles go through two buffers: the next tile is in flight (cp.async) while this one is multiplied; rows past the last
+  // key any row of the CTA sees are zero (a masked probability times a stale value must stay zero)
+  auto fetch = [&](int k0, int buf) {
+    bf16* Kd = Kb + buf * 64 * QP;
+    bf16* Vd = Vb + buf * 64 * VLD;
     for (int id = threadIdx.x; id < 64 * (DIM / 8); id += 128) {
       const int r = id / (DIM / 8), cc = id % (DIM / 8), j = k0 + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= kmax) v = *reinterpret_cast<const uint4*>(k_pages + ((long long)pt[j / page] * page + j % page) * krow + (long long)g * DIM + cc * 8);
-      *reinterpret_cast<uint4*>(Ks + r * QP + cc * 8) = v;
+      bf16* d = Kd + r * QP + cc * 8;
+      if (j <= kmax) cp_async16(d, k_pages + ((long long)pt[j / page] * page + j % page) * krow + (long long)g * DIM + cc * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
     for (int id = threadIdx.x; id < 64 * (VDIM / 8); id += 128) {
-      const int r = id % 64, cc = id / 64, j = k0 + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= kmax) v = *reinterpret_cast<const uint4*>(v_pages + ((long long)pt[j / page] * page + j % page) * vrow + (long long)g * VDIM + cc * 8);
-      const bf16* pv = reinterpret_cast<const bf16*>(&v);
-#pragma unroll
-      for (int x = 0; x < 8; ++x) Vt[(cc * 8 + x) * VP + r] = pv[x];
+      const int r = id / (VDIM / 8), cc = id % (VDIM / 8), j = k0 + r;
+      bf16* d = Vd + r * VLD + cc * 8;
+      if (j <= kmax) cp_async16(d, v_pages + ((long long)pt[j / page] * page + j % page) * vrow + (long long)g * VDIM + cc * 8);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
+  };
+  const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;  // this lane's row of a 16-key x 16-column block
+  int cur = 0;
+  fetch(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int k0 = 0; k0 <= kmax; k0 += 64, cur ^= 1) {
+    if (k0 + 64 <= kmax) fetch(k0 + 64, cur ^ 1);  // that buffer was released by the barrier at the end of the last iteration
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    if (k0 > wlim) continue;
+    const bf16* Ks = Kb + cur * 64 * QP;
+    const bf16* Vs = Vb + cur * 64 * VLD;
+    if (k0 <= wlim) {  // else: every row of this warp is past its causal limit
     float sacc[8][4];
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb) {
@@ -166,15 +191,21 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
       split3(sacc[2 * kk][2], sacc[2 * kk][3], a1[1], a2[1], a3[1]);
       split3(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], a1[2], a2[2], a3[2]);
       split3(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], a1[3], a2[3], a3[3]);
+      const bf16* vbase = Vs + (kk * 16 + lm_key) * VLD + lm_col;
 #pragma unroll
-      for (int nv = 0; nv < NV; ++nv) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Vt + (nv * 8 + gq) * VP + kk * 16 + 2 * tq);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Vt + (nv * 8 + gq) * VP + kk * 16 + 8 + 2 * tq);
-        mma16816(oacc[nv], a1, b0, b1);
-        mma16816(oacc[nv], a2, b0, b1);
-        mma16816(oacc[nv], a3, b0, b1);
+      for (int np = 0; np < NV / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, vbase + np * 16);
+        mma16816(oacc[2 * np], a1, b0, b1);
+        mma16816(oacc[2 * np], a2, b0, b1);
+        mma16816(oacc[2 * np], a3, b0, b1);
+        mma16816(oacc[2 * np + 1], a1, b2, b3);
+        mma16816(oacc[2 * np + 1], a2, b2, b3);
+        mma16816(oacc[2 * np + 1], a3, b2, b3);
       }
     }
+    }
+    __syncthreads();  // every warp is done with this buffer before the next iteration refills it
   }
   l_l += __shfl_xor_sync(0xffffffffu, l_l, 1); l_l += __shfl_xor_sync(0xffffffffu, l_l, 2);
   l_h += __shfl_xor_sync(0xffffffffu, l_h, 1); l_h += __shfl_xor_sync(0xffffffffu, l_h, 2);
@@ -213,16 +244,6 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 // With several key splits the (max, sum, accumulator) triples go to `partial` in the layout of pg_attn_decode and its merge
 // kernel finishes the rows.
 // ---------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const bf16* p) {
-  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
-}
-
-__device__ __forceinline__ void cp_async16(bf16* smem_dst, const bf16* gmem_src) {
-  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem_src) : "memory");
-}
-
 template <int DIM, int VDIM>
 __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                                                                      const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
@@ -388,7 +409,7 @@ int launch_latent(const void* q, const void* pages, const void* gate, long long 
 template <int DIM, int VDIM>
 int launch(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0, const int* n, const int* ctx,
            const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, int gate_per_head, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * 64 * (DIM + 8) + (size_t)VDIM * 72) * sizeof(bf16);
+  const size_t smem = ((size_t)3 * 64 * (DIM + 8) + (size_t)2 * 64 * (VDIM + 8)) * sizeof(bf16);
   auto kern = attn_ragged_mma_kernel<DIM, VDIM>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   dim3 grid((max_n * (H / G) + 63) / 64, G, entries);
