@@ -90,6 +90,7 @@ SIGNATURES = {
     "pg_moe_plan": [p, p, p, p, p, p, p, i32, i32, i32, p],
     "pg_moe_gemm": [p, i64, p, i32, p, i64, i64, p, i64, p, i32, i32, i32, i32, i32, i32, i64, i64, p],
     "pg_moe_gather_rows": [p, i64, p, p, i32, p, i64, i32, i32, i32, p],
+    "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, p],
     "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
 }
 _RESTYPE = {"pg_launch_count": i64}

@@ -396,12 +396,18 @@ def run_pukerax(args):
 
             k[f"moe_route_plan_{name}"] = dict(s=timed(route, flush=flush), bytes=T * (ff.n_all * 4 + ff.top * 16))
             ids, wts, plan = route()
+            counts = seq_ops.moe_route(z, ff.correction, ff.n_real, ff.top, ff.group_count, ff.group_keep, ff.scale)[2]
             real = int((ids < ff.n_real).sum())
-            mid, eo = prec.empty(plan.pairs, ff.F), torch.empty(plan.pairs, W, device="cuda", dtype=torch.float32)
             wbytes = 2 * ff.n_real * ff.F * W * 2
-            k[f"moe_expert_products_{name}"] = dict(
-                s=timed(lambda: (seq_ops.moe_gemm(h, plan, ff.w_up, mid, gather=True, act=seq_ops.ACT_RELU2), seq_ops.moe_gemm(mid, plan, ff.w_down, eo, gather=False)),
-                        flush=flush), flops=4 * real * ff.F * W, bytes=wbytes + real * (W * 2 + ff.F * 4 + W * 4))
+            # the path the model takes at this size (prompt: one dense run per expert on tcgen05; decode: the grouped kernel)
+            k[f"moe_expert_products_{name}"] = dict(s=timed(lambda: ff.expert_products(h, plan, counts, prec), flush=flush), flops=4 * real * ff.F * W,
+                                                    bytes=wbytes + real * (W * 2 + ff.F * 4 + W * 4))
+            if name == "prefill":
+                mid, eo2 = prec.empty(plan.pairs, ff.F), torch.empty(plan.pairs, W, device="cuda", dtype=torch.float32)
+                k["moe_grouped_kernel_prefill"] = dict(
+                    s=timed(lambda: (seq_ops.moe_gemm(h, plan, ff.w_up, mid, gather=True, act=seq_ops.ACT_RELU2), seq_ops.moe_gemm(mid, plan, ff.w_down, eo2, gather=False)),
+                            flush=flush), flops=4 * real * ff.F * W)
+            eo = ff.expert_products(h, plan, counts, prec)
             yy = torch.empty(T, W, device="cuda")
             k[f"moe_combine_{name}"] = dict(s=timed(lambda: seq_ops.moe_combine(eo, plan, ids, wts, h, y, yy), flush=flush), bytes=T * W * (ff.top * 4 + 4 + 4 + 2))
         for i in range(n_seq):

@@ -452,6 +452,68 @@ extern "C" int pg_moe_gather_rows(const void* x, long long ldx, const int* sorte
   PG_RET();
 }
 
+// Every expert's run of gathered rows through two dense tensor-core products (tcgen05 kernels of pg_gemm_bf16), issued from
+// here so that a layer costs one call from the host: mid = relu(xg W_up^T)^2 (bf16), eo = mid W_down^T (fp32).  One run is a few
+// dozen output tiles -- a fraction of the SMs -- so the experts are spread over four side streams that fork from and join the
+// caller's stream (the two products of one expert stay in order on one of them).
+namespace {
+constexpr int kSideStreams = 4;
+struct SideStreams {
+  cudaStream_t s[kSideStreams];
+  cudaEvent_t fork, join[kSideStreams];
+  bool ok = false;
+};
+SideStreams* side_streams() {
+  static SideStreams per_device[16];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  SideStreams& ss = per_device[dev];
+  if (!ss.ok) {
+    if (cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int i = 0; i < kSideStreams; ++i)
+      if (cudaStreamCreateWithFlags(&ss.s[i], cudaStreamNonBlocking) != cudaSuccess ||
+          cudaEventCreateWithFlags(&ss.join[i], cudaEventDisableTiming) != cudaSuccess)
+        return nullptr;
+    ss.ok = true;
+  }
+  return &ss;
+}
+}  // namespace
+
+extern "C" int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up, const void* w_down, void* mid, long long ldm, float* eo, long long ldo,
+                                 const int* counts_host, int n_real, int D, int F, void* stream) {
+  if (n_real <= 0 || D <= 0 || F <= 0 || counts_host == nullptr) return PG_ERR_ARG;
+  const bf16* x = static_cast<const bf16*>(xg);
+  const bf16* wu = static_cast<const bf16*>(w_up);
+  const bf16* wd = static_cast<const bf16*>(w_down);
+  bf16* m = static_cast<bf16*>(mid);
+  cudaStream_t main_st = PG_ST(stream);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  SideStreams* ss = nullptr;
+  if (cudaStreamIsCapturing(main_st, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) ss = side_streams();
+  if (ss != nullptr) {
+    if (cudaEventRecord(ss->fork, main_st) != cudaSuccess) return PG_ERR_CUDA;
+    for (int i = 0; i < kSideStreams; ++i)
+      if (cudaStreamWaitEvent(ss->s[i], ss->fork, 0) != cudaSuccess) return PG_ERR_CUDA;
+  }
+  long long off = 0;
+  int rc = PG_OK, used = 0;
+  for (int e = 0; e < n_real && rc == PG_OK; ++e) {
+    const int c = counts_host[e];
+    if (c <= 0) continue;
+    void* st = ss != nullptr ? static_cast<void*>(ss->s[used++ % kSideStreams]) : stream;
+    const int swap = c <= 128 ? 1 : 0;
+    rc = pg_gemm_bf16(x + off * ldx, ldx, wu + (long long)e * F * D, D, m + off * ldm, ldm, nullptr, nullptr, 0, c, F, D, PG_EPI_BF16, 2, 1.0f, swap, 1, st);
+    if (rc == PG_OK)
+      rc = pg_gemm_bf16(m + off * ldm, ldm, wd + (long long)e * D * F, F, eo + off * ldo, ldo, nullptr, nullptr, 0, c, D, F, PG_EPI_F32, 0, 1.0f, swap, 1, st);
+    off += c;
+  }
+  if (ss != nullptr)  // join even after an error: the caller's stream must not run ahead of work already issued
+    for (int i = 0; i < kSideStreams; ++i)
+      if (cudaEventRecord(ss->join[i], ss->s[i]) != cudaSuccess || cudaStreamWaitEvent(main_st, ss->join[i], 0) != cudaSuccess) return PG_ERR_CUDA;
+  return rc;
+}
+
 extern "C" int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
                               long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream) {
   if (tokens <= 0 || D <= 0 || top <= 0) return PG_ERR_ARG;

@@ -11,6 +11,7 @@ Every sub-layer gets its weights from a name -> tensor dict (`take(name)` pops a
 `Precision`, says what it keeps per sequence (`cache_spec`), and maps the step's rows h [T, D] (activation type) to
 y [T, D] fp32; the block around it owns norms and the residual stream.
 """
+import ctypes as C
 import math
 
 import torch
@@ -302,28 +303,29 @@ class RoutedFeedForward:
         return (not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
                 and not torch.cuda.is_current_stream_capturing())
 
+    def expert_products(self, h, plan, counts, prec):
+        """fp32 rows [pairs, D] in the plan's sorted order: down(relu(up h)^2) of every (token, real expert) pair."""
+        T = h.shape[0]
+        if self._dense_segments(T, prec):
+            # many rows per expert (prompt portions): the pair counts come to the host once per layer, every expert's tokens are
+            # gathered into one contiguous run and each expert is two dense tcgen05 products on its run
+            per = (C.c_int * self.n_real)(*counts.tolist())
+            xg = seq_ops.moe_gather_rows(h, plan, prec.empty(plan.pairs, self.D))
+            mid = prec.empty(plan.pairs, self.F)
+            eo = torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32)
+            _lib.check(_lib.lib().pg_moe_dense_runs(xg.data_ptr(), xg.stride(0), self.w_up.data_ptr(), self.w_down.data_ptr(), mid.data_ptr(), mid.stride(0),
+                                                    eo.data_ptr(), eo.stride(0), C.addressof(per), self.n_real, self.D, self.F, _lib.stream()),
+                       "pg_moe_dense_runs")
+            return eo
+        mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_RELU2)
+        return seq_ops.moe_gemm(mid, plan, self.w_down, torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32), gather=False)
+
     def __call__(self, h, b, prec):
         T = h.shape[0]
         z = seq_ops.linear(h, self.w_router, torch.empty(T, self.w_router.shape[0], device="cuda", dtype=torch.float32))
         ids, wts, counts = seq_ops.moe_route(z[:, :self.n_all], self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
         plan = seq_ops.MoePlan(ids, counts, max(1, self.n_real))
-        eo = None
-        if self.n_real and self._dense_segments(T, prec):
-            # many rows per expert (prompt portions): the pair counts come to the host once per layer, every expert's tokens are
-            # gathered into one contiguous run and each expert is two dense tcgen05 products on its run
-            per = counts.tolist()
-            xg = seq_ops.moe_gather_rows(h, plan, prec.empty(plan.pairs, self.D))
-            mid = prec.empty(plan.pairs, self.F)
-            eo = torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32)
-            off = 0
-            for e, c in enumerate(per):
-                if c:
-                    seq_ops.linear(xg[off:off + c], self.w_up[e], mid[off:off + c], act=seq_ops.ACT_RELU2)
-                    seq_ops.linear(mid[off:off + c], self.w_down[e], eo[off:off + c])
-                    off += c
-        elif self.n_real:
-            mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_RELU2)
-            eo = seq_ops.moe_gemm(mid, plan, self.w_down, torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32), gather=False)
+        eo = self.expert_products(h, plan, counts, prec) if self.n_real else None
         sh = self.shared(h, b, prec) if self.shared is not None else None
         return seq_ops.moe_combine(eo, plan, ids, wts, h, sh, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
 
