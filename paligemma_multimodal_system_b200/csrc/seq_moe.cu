@@ -81,10 +81,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
   __syncwarp();
   if (group_count > 1 && group_keep < group_count) {
-    // lane <-> group (rounds of 32): best choice score of the group; the kept groups are marked by negating nothing -- the
-    // dropped ones get -inf choice scores afterwards
+    // group g lives in lane g % 32, slot g / 32 (up to 8 slots = 256 groups): its score is its best choice score; group_keep rounds of
+    // a warp arg-max mark the kept groups, the others get -inf choice scores (not 0: choice scores can be negative)
     const int per = n_all / group_count;
-    // group scores into registers of the owning lanes (group g -> lane g % 32, slot g / 32); up to 8 slots = 256 groups
     float gs[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -94,7 +93,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
         for (int i = 0; i < per; ++i) b = fmaxf(b, choice[g * per + i]);
       gs[k] = b;
     }
-    unsigned keepmask[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // bit `lane` of slot k, only meaningful in the owning lane
+    unsigned keepmask[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // slot k kept (meaningful in the owning lane only)
     for (int r = 0; r < group_keep; ++r) {
       float bv = -INFINITY;
       int bi = 0x7fffffff;
@@ -242,31 +241,39 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x,
 }
 
 // The same product for bf16 operands on the tensor cores (mma.sync m16n8k16, fp32 accumulation): tile = 64 sorted rows of one
-// expert x 128 (or 64) features, 4 warps of 32 x 64 (32), k in steps of 64 through shared memory; the next step's operands are fetched into
-// registers (16-byte loads; the x rows are gathered through the sorted order) while the current one is multiplied.
+// expert x 128 (or 64) features, 4 warps of 32 x 64 (32), k in steps of 64 through a three-slot shared-memory ring filled by
+// cp.async (16-byte pieces; the x rows are gathered through the sorted order), two steps in flight while one is multiplied.
 __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async_16(bf16* smem_dst, const bf16* gmem_src) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem_src) : "memory");
+}
+
+constexpr int MOE_KT = 64;           // k step of the tensor-core kernel
+constexpr int MOE_LD = MOE_KT + 8;   // bf16 elements per shared row (conflict-free fragment reads)
+constexpr int MOE_STAGES = 3;        // k steps in flight (cp.async ring)
+
 template <typename TO, int BN>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ sorted_pair, int src_div,
                                                            const bf16* __restrict__ w, long long expert_stride, long long ldw, TO* __restrict__ out,
                                                            long long ldo, const int* __restrict__ plan, int F, int K, int act, long long x_off,
                                                            long long out_off) {
-  constexpr int KT = 64;      // k step
-  constexpr int LD = KT + 8;  // bf16 elements per shared row (conflict-free fragment reads)
-  constexpr int NI = BN / 16; // 8-feature blocks per warp (two warps side by side)
-  constexpr int CA = MOE_TILE * (KT / 8) / 128, CB = BN * (KT / 8) / 128;  // 16-byte chunks per thread and k step
+  constexpr int KT = MOE_KT, LD = MOE_LD, ST = MOE_STAGES;
+  constexpr int NI = BN / 16;  // 8-feature blocks per warp (two warps side by side)
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int e = plan[4 + 3 * tile], r0 = plan[4 + 3 * tile + 1], nr = plan[4 + 3 * tile + 2];
   const int f0 = blockIdx.x * BN;
   x += e * x_off;
   out += e * out_off;
-  __shared__ __align__(16) bf16 As[MOE_TILE * LD];
-  __shared__ __align__(16) bf16 Bs[BN * LD];
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  bf16* As = reinterpret_cast<bf16*>(moe_smem);  // [ST][MOE_TILE][LD]
+  bf16* Bs = As + ST * MOE_TILE * LD;            // [ST][BN][LD]
   __shared__ long long src[MOE_TILE];
   if (threadIdx.x < MOE_TILE) {
     long long s = -1;
@@ -277,20 +284,22 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
   const bf16* we = w + (long long)e * expert_stride;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   const int wm = warp >> 1, wn = warp & 1;
-  // chunk id -> row id / 8, columns 8 (id % 8)
-  uint4 ra[CA], rb[CB];
-  auto fetch = [&](int k0) {
-#pragma unroll
-    for (int j = 0; j < CA; ++j) {
-      const int id = threadIdx.x + 128 * j, r = id >> 3, c = (id & 7) * 8;
-      ra[j] = make_uint4(0, 0, 0, 0);
-      if (src[r] >= 0 && k0 + c < K) ra[j] = *reinterpret_cast<const uint4*>(x + src[r] * ldx + k0 + c);
+  // one k step of both operands into ring slot `stage`: 16-byte pieces, id -> row id / 8, columns 8 (id % 8); rows that do not
+  // exist and columns past K are zeros
+  auto issue = [&](int k0, int stage) {
+    bf16* Ad = As + stage * MOE_TILE * LD;
+    bf16* Bd = Bs + stage * BN * LD;
+    for (int id = threadIdx.x; id < MOE_TILE * (KT / 8); id += 128) {
+      const int r = id >> 3, c = (id & 7) * 8;
+      bf16* d = Ad + r * LD + c;
+      if (src[r] >= 0 && k0 + c < K) cp_async_16(d, x + src[r] * ldx + k0 + c);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
-#pragma unroll
-    for (int j = 0; j < CB; ++j) {
-      const int id = threadIdx.x + 128 * j, r = id >> 3, c = (id & 7) * 8;
-      rb[j] = make_uint4(0, 0, 0, 0);
-      if (f0 + r < F && k0 + c < K) rb[j] = *reinterpret_cast<const uint4*>(we + (long long)(f0 + r) * ldw + k0 + c);
+    for (int id = threadIdx.x; id < BN * (KT / 8); id += 128) {
+      const int r = id >> 3, c = (id & 7) * 8;
+      bf16* d = Bd + r * LD + c;
+      if (f0 + r < F && k0 + c < K) cp_async_16(d, we + (long long)(f0 + r) * ldw + k0 + c);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
   };
   float acc[2][NI][4];
@@ -298,27 +307,25 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
   for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
     for (int ni = 0; ni < NI; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
-  fetch(0);
-  for (int k0 = 0; k0 < K; k0 += KT) {
-    __syncthreads();  // the previous step's fragments have been read
+  const int nk = (K + KT - 1) / KT;
 #pragma unroll
-    for (int j = 0; j < CA; ++j) {
-      const int id = threadIdx.x + 128 * j;
-      *reinterpret_cast<uint4*>(As + (id >> 3) * LD + (id & 7) * 8) = ra[j];
-    }
-#pragma unroll
-    for (int j = 0; j < CB; ++j) {
-      const int id = threadIdx.x + 128 * j;
-      *reinterpret_cast<uint4*>(Bs + (id >> 3) * LD + (id & 7) * 8) = rb[j];
-    }
-    __syncthreads();
-    if (k0 + KT < K) fetch(k0 + KT);
+  for (int s = 0; s < ST - 1; ++s) {
+    if (s < nk) issue(s * KT, s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(ST - 2) : "memory");  // k step kt has landed
+    __syncthreads();                                                    // ... for every thread; slot (kt - 1) % ST is free again
+    if (kt + ST - 1 < nk) issue((kt + ST - 1) * KT, (kt + ST - 1) % ST);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const bf16* Ac = As + (kt % ST) * MOE_TILE * LD;
+    const bf16* Bc = Bs + (kt % ST) * BN * LD;
 #pragma unroll
     for (int ks = 0; ks < KT / 16; ++ks) {
       uint32_t a[2][4];
 #pragma unroll
       for (int mi = 0; mi < 2; ++mi) {
-        const bf16* ap = As + (32 * wm + 16 * mi + gq) * LD + ks * 16 + 2 * tq;
+        const bf16* ap = Ac + (32 * wm + 16 * mi + gq) * LD + ks * 16 + 2 * tq;
         a[mi][0] = *reinterpret_cast<const uint32_t*>(ap);
         a[mi][1] = *reinterpret_cast<const uint32_t*>(ap + 8 * LD);
         a[mi][2] = *reinterpret_cast<const uint32_t*>(ap + 8);
@@ -326,7 +333,7 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
       }
 #pragma unroll
       for (int ni = 0; ni < NI; ++ni) {
-        const bf16* bp = Bs + ((BN / 2) * wn + 8 * ni + gq) * LD + ks * 16 + 2 * tq;
+        const bf16* bp = Bc + ((BN / 2) * wn + 8 * ni + gq) * LD + ks * 16 + 2 * tq;
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(bp), b1 = *reinterpret_cast<const uint32_t*>(bp + 8);
         mma_bf16_16816(acc[0][ni], a[0], b0, b1);
         mma_bf16_16816(acc[1][ni], a[1], b0, b1);
@@ -346,6 +353,18 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
           stm(out, (long long)(r0 + r) * ldo + f, v);
         }
       }
+}
+
+template <typename TO, int BN>
+static int launch_moe_mma(dim3 grid, cudaStream_t st, const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride,
+                          long long ldw, void* out, long long ldo, const int* plan, int F, int K, int act, long long x_off, long long out_off) {
+  const size_t smem = (size_t)MOE_STAGES * (MOE_TILE + BN) * MOE_LD * sizeof(bf16);
+  auto kern = moe_gemm_mma_kernel<TO, BN>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+  kern<<<grid, 128, smem, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw, static_cast<TO*>(out), ldo,
+                                plan, F, K, act, x_off, out_off);
+  pg_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
 
 // xg[row, :] = x[sorted_pair[row] / top, :] for the `rows` sorted pairs that exist (rows read from offsets[n_real] on the device)
@@ -420,12 +439,10 @@ extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair,
     const int BN = narrow ? 64 : 128;
     dim3 g2((F + BN - 1) / BN, max_tiles);
 #define PG_MOE_MMA(TO, BNV) \
-  moe_gemm_mma_kernel<TO, BNV><<<g2, 128, 0, st>>>(static_cast<const bf16*>(x), ldx, sorted_pair, src_div, static_cast<const bf16*>(w), expert_stride, ldw, \
-                                                   static_cast<TO*>(out), ldo, plan, F, K, act, x_expert_off, out_expert_off)
+  return launch_moe_mma<TO, BNV>(g2, st, x, ldx, sorted_pair, src_div, w, expert_stride, ldw, out, ldo, plan, F, K, act, x_expert_off, out_expert_off)
     if (out_f32) { if (narrow) PG_MOE_MMA(float, 64); else PG_MOE_MMA(float, 128); }
     else { if (narrow) PG_MOE_MMA(bf16, 64); else PG_MOE_MMA(bf16, 128); }
 #undef PG_MOE_MMA
-    PG_RET();
   }
   if (in_f32 && out_f32)
     moe_gemm_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, sorted_pair, src_div, static_cast<const float*>(w), expert_stride,
