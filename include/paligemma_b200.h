@@ -376,7 +376,7 @@ int pg_linear_attn_chunked(const void* qkv, long long ld, float* state, const fl
                            const int* entry_n, const int* entry_ctx, const int* entry_slot, int entries, int H, int dim, int vdim,
                            int act_f32, void* stream);
 
-/* ---- multi-stream residual ("hyper-connections"): xs fp32 [rows, S, D], S <= 8 -------------------------------------------------
+/* ---- multi-stream residual ("hyper-connections"): xs fp32 [rows, S, D], S <= 16 ------------------------------------------------
  * pg_embed_streams: xs[t, s, :] = table[tokens[t], 0:D] * scale for every stream s.
  * pg_stream_mix_norm, per row, in this order:
  *   y != NULL:         x_to <- sum_s mix[s * S + to] x_s + write_coef[to] * y[t, :]   (all streams from the old ones, in place)

@@ -17,7 +17,7 @@ using bf16 = __nv_bfloat16;
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 template <typename T>
 __device__ __forceinline__ float ld_t(const T* p, long long i);
@@ -41,7 +41,7 @@ __global__ void embed_streams_kernel(const int* __restrict__ tokens, const TI* _
 
 // One CTA per token row.  A thread holds V consecutive columns of all S streams (V = 4: 16-byte accesses): the write-back is
 // column-wise, so it is done in place.  u goes to shared memory for the second pass after the block-wide mean square.
-// SMAX = 4 or 8 bounds the unrolled stream loops.
+// SMAX = 4, 8 or 16 bounds the unrolled stream loops.
 template <int V>
 struct VecF;
 template <>
@@ -182,11 +182,13 @@ extern "C" int pg_stream_mix_norm(float* xs, const float* y, long long ldy, cons
                    (reinterpret_cast<uintptr_t>(out_act) & (out_f32 ? 15 : 7)) == 0;
 #define PG_STREAM(TO, V, SM) return launch_stream<TO, V, SM>(xs, y, ldy, mix, write_coef, read_coef, norm_w, out_act, rows, S, D, eps, smem, st)
   if (out_f32) {
+    if (S > 8) PG_STREAM(float, 1, 16);
     if (vec && S <= 4) PG_STREAM(float, 4, 4);
     if (vec) PG_STREAM(float, 4, 8);
     if (S <= 4) PG_STREAM(float, 1, 4);
     PG_STREAM(float, 1, 8);
   }
+  if (S > 8) PG_STREAM(bf16, 1, 16);
   if (vec && S <= 4) PG_STREAM(bf16, 4, 4);
   if (vec) PG_STREAM(bf16, 4, 8);
   if (S <= 4) PG_STREAM(bf16, 1, 4);

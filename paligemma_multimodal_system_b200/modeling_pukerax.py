@@ -34,8 +34,8 @@ class PukeraxConfig:
         self.norm_eps = float(cfg["norm"]["eps"])
         self.hyper = "streams" in cfg
         self.streams = int(cfg.get("streams", 1))
-        if not 1 <= self.streams <= 8:
-            raise ValueError("streams must be between 1 and 8")
+        if not 1 <= self.streams <= 16:
+            raise ValueError("streams must be between 1 and 16")
         self.layers: List[dict] = list(cfg["layers"])
         for i, l in enumerate(self.layers):
             if l["type"] != "latent_attention":

@@ -42,7 +42,7 @@ def test_config_and_cache_layout():
     with pytest.raises(ValueError):
         PukeraxConfig(bad)
     with pytest.raises(ValueError):
-        PukeraxConfig(dict(_cfg(), streams=9))
+        PukeraxConfig(dict(_cfg(), streams=17))
 
 
 def test_weight_loading_checks_names_and_shapes():

@@ -112,7 +112,7 @@ def _one_entry(spec, T, dtype, ctx=0):
 # ----------------------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ----------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("S,D", [(1, 40), (2, 33), (4, 96), (8, 130)])
+@pytest.mark.parametrize("S,D", [(1, 40), (2, 33), (4, 96), (8, 130), (12, 64)])
 @pytest.mark.parametrize("f32", [True, False])
 def test_stream_write_back_and_normalised_read(S, D, f32):
     from paligemma_multimodal_system_b200 import seq_ops
