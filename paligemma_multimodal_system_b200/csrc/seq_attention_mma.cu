@@ -244,14 +244,15 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 // With several key splits the (max, sum, accumulator) triples go to `partial` in the layout of pg_attn_decode and its merge
 // kernel finishes the rows.
 // ---------------------------------------------------------------------------------------------------------------------
-template <int DIM, int VDIM>
+template <int DIM, int VDIM, int KT>
 __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                                                                      const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                                      float* __restrict__ partial, const int* __restrict__ entry_row0,
                                                                      const int* __restrict__ entry_n, const int* __restrict__ entry_ctx,
                                                                      const int* __restrict__ page_table, int max_pages, int page, int H, float scale) {
   constexpr int KS = DIM / 16, NV = VDIM / 8, LD = DIM + 8;
-  static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && VDIM <= DIM, "tile shapes");
+  static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && VDIM <= DIM && (KT == 32 || KT == 64), "tile shapes");
+  constexpr int NB = KT / 8;  // 8-key blocks per tile
   const int e = blockIdx.z, h0 = blockIdx.y * 64, split = blockIdx.x, nsplit = gridDim.x;
   if (entry_n[e] != 1) return;
   const int ctx = entry_ctx[e];
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   const int nrows = (blockDim.x >> 5) * 16;
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);  // [nrows][LD]
-  bf16* Kbuf = Qs + nrows * LD;               // two key tiles [64][LD]: the next one is fetched (cp.async) while this one is used
+  bf16* Kbuf = Qs + nrows * LD;               // two key tiles [KT][LD]: the next one is fetched (cp.async) while this one is used
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
   for (int id = threadIdx.x; id < nrows * (DIM / 8); id += blockDim.x) {
     const int r = id / (DIM / 8), cc = id % (DIM / 8);
@@ -273,13 +274,13 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
   float m_l = -INFINITY, m_h = -INFINITY, l_l = 0.f, l_h = 0.f;
   const int* pt = page_table + (long long)e * max_pages;
-  const int ntiles = ctx / 64 + 1;  // keys 0 .. ctx
+  const int ntiles = ctx / KT + 1;  // keys 0 .. ctx
   const float sc2 = scale * 1.4426950408889634f;
   // lane's row address inside a 16-key x 16-column block for ldmatrix.x4.trans: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15)
   const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
   auto fetch_tile = [&](int it, bf16* dst) {
-    const int k0 = it * 64;
-    for (int id = threadIdx.x; id < 64 * (DIM / 8); id += blockDim.x) {
+    const int k0 = it * KT;
+    for (int id = threadIdx.x; id < KT * (DIM / 8); id += blockDim.x) {
       const int r = id / (DIM / 8), cc = id % (DIM / 8), j = k0 + r;
       bf16* d = dst + r * LD + cc * 8;
       if (j <= ctx) cp_async16(d, pages + ((long long)pt[j / page] * page + j % page) * DIM + cc * 8);
@@ -290,15 +291,15 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   if (split < ntiles) fetch_tile(split, Kbuf);
   asm volatile("cp.async.commit_group;" ::: "memory");
   for (int it = split; it < ntiles; it += nsplit) {
-    const int k0 = it * 64;
-    const bf16* Ks = Kbuf + cur * 64 * LD;
-    if (it + nsplit < ntiles) fetch_tile(it + nsplit, Kbuf + (cur ^ 1) * 64 * LD);  // that buffer was released by the barrier below
+    const int k0 = it * KT;
+    const bf16* Ks = Kbuf + cur * KT * LD;
+    if (it + nsplit < ntiles) fetch_tile(it + nsplit, Kbuf + (cur ^ 1) * KT * LD);  // that buffer was released by the barrier below
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group has landed: this tile
     __syncthreads();
-    float sacc[8][4];
+    float sacc[NB][4];
 #pragma unroll
-    for (int nb = 0; nb < 8; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+    for (int nb = 0; nb < NB; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
 #pragma unroll 2
     for (int ks = 0; ks < KS; ++ks) {
       uint32_t a[4];
@@ -307,7 +308,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
       a[2] = *reinterpret_cast<const uint32_t*>(Qs + rl * LD + ks * 16 + 8 + 2 * tq);
       a[3] = *reinterpret_cast<const uint32_t*>(Qs + rh * LD + ks * 16 + 8 + 2 * tq);
 #pragma unroll
-      for (int nb = 0; nb < 8; ++nb) {
+      for (int nb = 0; nb < NB; ++nb) {
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Ks + (nb * 8 + gq) * LD + ks * 16 + 2 * tq);
         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Ks + (nb * 8 + gq) * LD + ks * 16 + 8 + 2 * tq);
         mma16816(sacc[nb], a, b0, b1);
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
     }
     float mx_l = -INFINITY, mx_h = -INFINITY;
 #pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
+    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = k0 + nb * 8 + 2 * tq + (c & 1);
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
     const float corr_l = exp2f(m_l - mn_l), corr_h = exp2f(m_h - mn_h);
     float sum_l = 0.f, sum_h = 0.f;
 #pragma unroll
-    for (int nb = 0; nb < 8; ++nb)
+    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float p = exp2f(sacc[nb][c] - ((c & 2) ? mn_h : mn_l));
@@ -345,7 +346,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
       oacc[nv][0] *= corr_l; oacc[nv][1] *= corr_l; oacc[nv][2] *= corr_h; oacc[nv][3] *= corr_h;
     }
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
+    for (int kk = 0; kk < KT / 16; ++kk) {
       uint32_t a1[4], a2[4], a3[4];
       split3(sacc[2 * kk][0], sacc[2 * kk][1], a1[0], a2[0], a3[0]);
       split3(sacc[2 * kk][2], sacc[2 * kk][3], a1[1], a2[1], a3[1]);
@@ -393,17 +394,26 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   }
 }
 
-template <int DIM, int VDIM>
-int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
-                  const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, cudaStream_t st) {
-  const int warps = H >= 64 ? 4 : (H + 15) / 16;
-  const size_t smem = ((size_t)(16 * warps + 2 * 64) * (DIM + 8)) * sizeof(bf16);
-  auto kern = attn_latent_decode_mma_kernel<DIM, VDIM>;
+template <int DIM, int VDIM, int KT>
+int launch_latent_kt(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
+                     const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int warps, cudaStream_t st) {
+  const size_t smem = ((size_t)(16 * warps + 2 * KT) * (DIM + 8)) * sizeof(bf16);
+  auto kern = attn_latent_decode_mma_kernel<DIM, VDIM, KT>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   kern<<<dim3(nsplit, (H + 63) / 64, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),
                                                                       ldg, static_cast<bf16*>(out), partial, row0, n, ctx, pt, max_pages, page, H, scale);
   pg_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+}
+
+// up to 32 heads = two warps per CTA: 32-key tiles keep four such CTAs on an SM (shared memory), 64-key tiles only two
+template <int DIM, int VDIM>
+int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
+                  const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, cudaStream_t st) {
+  const int warps = H >= 64 ? 4 : (H + 15) / 16;
+  if (warps <= 2)
+    return launch_latent_kt<DIM, VDIM, 32>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, warps, st);
+  return launch_latent_kt<DIM, VDIM, 64>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, warps, st);
 }
 
 template <int DIM, int VDIM>
