@@ -452,6 +452,9 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
   }
 }
 
+// one value column per thread up to 256 columns: the loop over the splits is a chain of dependent loads per column
+static inline int merge_threads(int vdim) { return vdim <= 64 ? 64 : vdim <= 128 ? 128 : 256; }
+
 template <typename TA>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
                                          const int* __restrict__ entry_row0, const int* __restrict__ entry_n, int H, int vdim, int nsplit,
@@ -868,7 +871,7 @@ static int launch_attn_decode(const void* q, const void* kp, const void* vp, con
                                                      H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head);
   pg_count_launch(1);
   if (nsplit > 1) {
-    attn_decode_merge_kernel<TA><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit,
+    attn_decode_merge_kernel<TA><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit,
                                                                   gate_per_head);
     pg_count_launch(1);
   }
@@ -880,10 +883,10 @@ extern "C" int pg_attn_decode_merge(const float* partial, const void* gate, long
   if (entries <= 0 || entries > 65535 || nsplit <= 0 || H <= 0 || vdim <= 0 || partial == nullptr) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
   if (act_f32)
-    attn_decode_merge_kernel<float><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const float*>(gate), ldg, static_cast<float*>(out), entry_row0, entry_n,
+    attn_decode_merge_kernel<float><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const float*>(gate), ldg, static_cast<float*>(out), entry_row0, entry_n,
                                                                      H, vdim, nsplit, gate_per_head);
   else
-    attn_decode_merge_kernel<bf16><<<dim3(H, entries), 64, 0, st>>>(partial, static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), entry_row0, entry_n, H,
+    attn_decode_merge_kernel<bf16><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), entry_row0, entry_n, H,
                                                                     vdim, nsplit, gate_per_head);
   PG_RET();
 }
